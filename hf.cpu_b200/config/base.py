@@ -74,6 +74,7 @@ class ModelPlan:
     final_norm: PartSpec
     head: PartSpec
     eos_token_ids: List[int] = field(default_factory=list)
+    streams: int = 1                        # copies of the residual stream (hyper-connections); 1: the plain stream
 
     def validate(self) -> None:
         for i, e in enumerate(self.schedule):

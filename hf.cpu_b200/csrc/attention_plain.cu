@@ -8,6 +8,10 @@
 // than query/key heads (d): the output row of a head has dv elements.  Consecutive value rows lie v_row elements apart:
 // dv for an array of values, d when the values are the first dv elements of the keys themselves (one latent row per
 // token that serves as key and, without its last elements, as value).
+//
+// Two options of the softmax: a sink per head, a score without key or value that joins the denominator once
+// (p_j = exp(s_j) / (exp(sink) + sum exp(s_j)); `sinks` [H] float32, learned, or `zero_sink` for a sink of score 0,
+// which adds one to the denominator), and a bias linear in the distance, s_j -= slopes[h] * (pos - j).
 #include "common.cuh"
 
 static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
@@ -22,7 +26,8 @@ template <typename T, int MAX_D_PER_LANE>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int32_t *block_table, int max_blocks,
                        const int32_t *token_seq, const int32_t *positions, int block_size, long long num_pages,
-                       int window, float scale, T *out, int H, int G, int d, int dv, int v_row, int *err)
+                       int window, float scale, T *out, int H, int G, int d, int dv, int v_row, const float *sinks, int zero_sink,
+                       const float *slopes, int *err)
 {
     pdl_sync();
     int t = blockIdx.x, h = blockIdx.y;
@@ -39,6 +44,7 @@ attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int
     for (int i = threadIdx.x; i < d; i += blockDim.x) sq[i] = to_f32(qr[i]);
     __syncthreads();
 
+    const float slope = slopes ? slopes[h] : 0.f;
     float m = -INFINITY, l = 0.f, acc[MAX_D_PER_LANE];
 #pragma unroll
     for (int i = 0; i < MAX_D_PER_LANE; i++) acc[i] = 0.f;
@@ -56,6 +62,7 @@ attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int
             if (c < d) dot = fmaf(sq[c], to_f32(k_cache[base + c]), dot);
         }
         dot = warp_sum(dot) * scale;
+        if (slopes) dot -= slope * (float)(pos - j);
         float m_new = fmaxf(m, dot);
         float corr = expf(m - m_new);            // exp(-inf) = 0 on the first key
         float p = expf(dot - m_new);
@@ -82,7 +89,14 @@ attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int
         f[w] = s_m[w] == -INFINITY ? 0.f : expf(s_m[w] - mm);
         ll += s_l[w] * f[w];
     }
-    float inv = ll > 0.f ? 1.0f / ll : 0.f;
+    float carry = 1.0f;                            // what the keys' share shrinks by when the sink is the largest score
+    if (sinks || zero_sink) {
+        const float sk = sinks ? sinks[h] : 0.f;
+        const float top = fmaxf(mm, sk);
+        carry = mm == -INFINITY ? 0.f : expf(mm - top);
+        ll = ll * carry + expf(sk - top);
+    }
+    float inv = ll > 0.f ? carry / ll : 0.f;
     T *o = out + ((size_t)t * H + h) * dv;
     for (int c = threadIdx.x; c < dv; c += blockDim.x) {
         float v = 0.f;
@@ -98,7 +112,8 @@ using namespace hfb;
 extern "C" int hfb_attention_plain(const void *q, const void *k_cache, const void *v_cache, int dt,
                                    const int32_t *block_table, int max_blocks, const int32_t *token_seq,
                                    const int32_t *positions, int block_size, int64_t num_pages, int window,
-                                   float scale, void *out, int T, int H, int G, int d, int dv, int v_row, hfb_stream s)
+                                   float scale, void *out, int T, int H, int G, int d, int dv, int v_row, const float *sinks,
+                                   int zero_sink, const float *slopes, hfb_stream s)
 {
     if (T <= 0) return HFB_OK;
     if (!valid_dt(dt) || H <= 0 || G <= 0 || H % G || block_size <= 0 || max_blocks <= 0 || v_row < dv)
@@ -110,7 +125,7 @@ extern "C" int hfb_attention_plain(const void *q, const void *k_cache, const voi
     const bool small = d <= 256 && dv <= 256;
 #define HFB_PLAIN_ATT(TY, L) \
     g_launch_err = launch_pdl(attention_plain_kernel<TY, L>, dim3(grid), dim3(ATT_WARPS * 32), 0, (cudaStream_t)s, (const TY *)q, (const TY *)k_cache, \
-        (const TY *)v_cache, block_table, max_blocks, token_seq, positions, block_size, num_pages, window, scale, (TY *)out, H, G, d, dv, v_row, error_word())
+        (const TY *)v_cache, block_table, max_blocks, token_seq, positions, block_size, num_pages, window, scale, (TY *)out, H, G, d, dv, v_row, sinks, zero_sink, slopes, error_word())
     if (dt == HFB_F32) { if (small) HFB_PLAIN_ATT(float, 8); else HFB_PLAIN_ATT(float, MAX_D_PER_LANE); }
     else { if (small) HFB_PLAIN_ATT(__nv_bfloat16, 8); else HFB_PLAIN_ATT(__nv_bfloat16, MAX_D_PER_LANE); }
 #undef HFB_PLAIN_ATT

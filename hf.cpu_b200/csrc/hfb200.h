@@ -113,7 +113,8 @@ int hfb_rope_kv_write(const void *qkv, int dt, const float *cos_sin, int n_rot, 
 int hfb_attention_plain(const void *q, const void *k_cache, const void *v_cache, int dt,
                         const int32_t *block_table, int max_blocks, const int32_t *token_seq,
                         const int32_t *positions, int block_size, int64_t num_pages, int window, float scale,
-                        void *out, int T, int H, int G, int d, int dv, int v_row, hfb_stream s);
+                        void *out, int T, int H, int G, int d, int dv, int v_row, const float *sinks, int zero_sink,
+                        const float *slopes, hfb_stream s);
 
 /* The same for bfloat16 with head_dim 64 or 128 and a block size that divides 64, tiled, on tensor cores.
  * Tiles (tile_seq, tile_t0 = first token index, tile_nt = tokens) cover the step's tokens; a tile holds at
@@ -160,6 +161,8 @@ int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, int interleaved,
 
 /* Activations: codes for hfb_glu / hfb_act / the expert products. */
 enum { HFB_ACT_SILU = 0, HFB_ACT_RELU = 1, HFB_ACT_GELU_TANH = 2, HFB_ACT_RELU2 = 3, HFB_ACT_NONE = 4 };
+/* added to the activation of hfb_moe_gemm: rows of w alternate gate, up, and out [.., N / 2] = act(gate) * up */
+enum { HFB_ACT_GLU = 256 };
 
 /* out[t, f] = act(g) * u, gate and up laid out as for hfb_swiglu */
 int hfb_glu(const void *gu, void *out, int dt, int T, int F, int interleaved, int act, hfb_stream s);
@@ -187,12 +190,13 @@ int hfb_dyt_residual(const void *y, int y_dt, int splits, const void *bias, int 
  * (float32 [d], shared by the heads; null: no weight) -> q_out [T, H d], keys [.., G, d] and values [.., G, dv] at cache
  * slot slots[t].  G == 0: the row holds queries only.  Values mixed across layers: v_mode 1 copies the row's values to
  * v_first [T, G dv] (float32) as they are; v_mode 2 replaces them by (1 - v_lambda) v + v_lambda v_first before they
- * are stored; 0: neither. */
+ * are stored; 0: neither.  pairing 0 rotates the pairs (i, i + n_rot/2), 1 the pairs (2i, 2i + 1).  dv == 0: the row has
+ * no value heads (src [splits, T, H d + G d]) and v_cache is not written. */
 int hfb_rope_norm_kv_write(const float *src, int splits, const void *bias, int bias_dt, const float *cos_sin,
                            int n_rot, int n_positions, const int32_t *positions, const int32_t *slots,
                            void *q_out, void *k_cache, void *v_cache, int out_dt, int64_t cache_slots, int T,
                            int H, int G, int d, int dv, int norm, float eps, const float *q_w, const float *k_w,
-                           float *v_first, int v_mode, float v_lambda, hfb_stream s);
+                           float *v_first, int v_mode, float v_lambda, int pairing, hfb_stream s);
 
 /* Latent attention, the tail of the down product: src [splits, T, q_rank + kv_rank + rot] float32 partial sums ->
  * query latent = rmsnorm(src[:q_rank]) * q_w -> cq_out [T, q_rank]; key/value latent = rmsnorm(next kv_rank) * kv_w ->
@@ -243,6 +247,52 @@ int hfb_moe_gemm(const void *a, int a_dt, const void *w, int w_dt, void *out, in
 
 /* out[t, :] = sum_j weights[t, j] * y[t * top + j, :] in float32, j in order */
 int hfb_moe_combine(const void *y, int y_dt, const float *weights, float *out, int T, int top, int N, hfb_stream s);
+
+/* The router of a mixture whose scores are a softmax over all router outputs: z [splits, T, E] float32 partial sums;
+ * s = softmax(z); choice score = s + correction (null: none); the outputs form n_groups equal groups of neighbours and
+ * only those of the `keep` groups with the largest choice score can be chosen; ids [T, top] = the `top` largest choice
+ * scores (largest first, the lower index among equals), weights = s[ids] * scale. */
+int hfb_moe_route_softmax(const float *z, int splits, const void *correction, int corr_dt, int T, int E, int top,
+                          int n_groups, int keep, float scale, int32_t *ids, float *weights, hfb_stream s);
+
+/* Hyper-connections: the residual stream in S copies, x [T, S, E] float32.
+ * hc_spread: every copy = emb [T, E].
+ * hc_in_norm: out[m, :] = norm(sum_s in_w[s] x[rows ? rows[m] : m, s, :]) with the Dynamic Tanh norm (alpha, w, b) of type
+ *   p_dt; in_w == NULL: the plain sum; alpha == NULL: no norm.
+ * hc_update: y = scale .* (factor_a * sum of ya's splits_a planes + factor_b * sum of yb's planes + sum_j mix_w[t, j] *
+ *   (mix_ids[t, j] >= n_real ? mix_h[t, :] : mix_y[t * top + j, :])), any of the three terms absent when its pointer is
+ *   null; then x'[t, d, :] = sum_s hc_mix[s, d] x[t, s, :] + hc_out[d] y for every copy d from the old copies, and, with
+ *   out != NULL, out[t, :] = norm(sum_d next_in[d] x'[t, d, :]) (next_in NULL: plain sum; alpha NULL: no norm). */
+int hfb_hc_spread(const float *emb, float *x, int S, int T, int E, hfb_stream s);
+int hfb_hc_in_norm(const float *x, int S, const float *in_w, const int32_t *rows, const void *alpha, const void *w,
+                   const void *b, int p_dt, void *out, int out_dt, int M, int E, hfb_stream s);
+int hfb_hc_update(float *x, int S, const float *ya, int splits_a, float factor_a, const float *yb, int splits_b,
+                  float factor_b, const float *mix_y, const float *mix_w, const int32_t *mix_ids, int top, int n_real,
+                  const void *mix_h, int mix_h_dt, const void *scale, int scale_dt, const float *hc_mix,
+                  const float *hc_out, const float *next_in, const void *alpha, const void *w, const void *b,
+                  int p_dt, void *out, int out_dt, int T, int E, hfb_stream s);
+
+/* Recurrent mixers (float32 throughout; a request's state lives in row seq_slots[seq] of a [n_slots, slot_stride] array).
+ * decay: out[t, h, i] = exp(-rate[h] * softplus(sign * (z[t, h, i] + bias[h, i]))), z the sum of `splits` planes
+ *   [T, z_stride] read from column z_col0 on.
+ * short_conv: causal convolution over time per channel (w [C, taps], last column = current token), silu, then unit
+ *   length for the first n_unit heads of a row made of n_a heads of d_a and n_b heads of d_b channels (the first n_scaled
+ *   of them also times `scale`); `carried` holds each request's last taps - 1 inputs and is brought up to date.
+ * linear_scan: per head S <- diag(a) S + k u^T, o = S^T q * q_scale with u = v, or, with beta_logit, u = sigmoid(beta)
+ *   (v - (diag(a) S)^T k); state [H, dv, d] per slot; rows of q, k (Hq heads), a, v, o (H heads) with their strides.
+ * gate_norm: out = o / sqrt(mean(o^2) + eps) * w * gate(g) per head; gate 0 silu, 1 sigmoid. */
+int hfb_decay(const float *z, int splits, int z_stride, int z_col0, const void *bias, int bias_dt, const float *rate,
+              float sign, float *out, int T, int H, int d, hfb_stream s);
+int hfb_short_conv(const float *x, int splits, const void *w, int w_dt, int taps, float *carried, int64_t slot_stride,
+                   const int32_t *token_seq, const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, int S,
+                   float *out, int T, int n_a, int d_a, int n_b, int d_b, int n_unit, int n_scaled, float scale,
+                   float unit_eps, hfb_stream s);
+int hfb_linear_scan(const float *q, int q_stride, const float *k, int k_stride, const float *v, int v_stride,
+                    const float *a, int a_stride, const float *beta_logit, int beta_stride, float q_scale,
+                    float *state, int64_t slot_stride, const int32_t *cu_tokens, const int32_t *seq_slots,
+                    int n_slots, int S, float *o, int o_stride, int H, int Hq, int d, int dv, hfb_stream s);
+int hfb_gate_norm(const float *o, const void *w, int w_dt, float eps, const float *g, int g_splits, int g_stride,
+                  int g_col0, int gate, void *out, int out_dt, int T, int H, int dv, hfb_stream s);
 
 /* out[m] = index of the first maximum of logits[m, :] */
 int hfb_argmax(const float *logits, int32_t *out, int M, int V, hfb_stream s);

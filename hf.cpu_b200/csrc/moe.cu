@@ -16,6 +16,15 @@ namespace hfb {
 
 constexpr int ROUTE_WARPS = 4;
 
+__device__ __forceinline__ float moe_act(float v, int act)
+{
+    if (act == HFB_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+    else if (act == HFB_ACT_RELU) v = fmaxf(v, 0.f);
+    else if (act == HFB_ACT_SILU) v = v / (1.0f + expf(-v));
+    else if (act == HFB_ACT_GELU_TANH) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    return v;
+}
+
 // The choice of experts from the router's logits z [splits, T, E] (float32: partial sums of the router's product,
 // summed in split order, plus its bias; finished logits have one split and no bias): one warp per token; the `top`
 // largest, the lower index among equals; weights = softmax over the chosen logits only.  smem per warp: E logits, `top`
@@ -59,6 +68,83 @@ moe_topk_kernel(const float *zs, int splits, const void *bias, int bias_dt, int 
         for (int j = 0; j < top; j++) { zc[j] = expf(zc[j] - m); sum += zc[j]; }
         const float inv = 1.0f / sum;
         for (int j = 0; j < top; j++) weights[(size_t)t * top + j] = zc[j] * inv;
+    }
+}
+
+// A router that scores with a softmax over all of its outputs and chooses among groups: z [splits, T, E] as above;
+// s = softmax(z) over all E; the choice score of an output is s + correction; the E outputs form `n_groups` equal groups
+// of neighbours, a group's score is its largest choice score, and only the outputs of the `keep` best groups can be
+// chosen (the lower group among equals); of those the `top` largest choice scores choose (the lower index among equals).
+// weights = s of the chosen (without the correction) * scale, not renormalised.  An index at or above the number of real
+// experts names an identity expert; whoever reads `ids` decides what that means.  One warp per token; smem per warp:
+// 2 E + n_groups floats.
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_softmax_kernel(const float *zs, int splits, const void *correction, int corr_dt, int T, int E, int top, int n_groups,
+                         int keep, float scale, int32_t *ids, float *weights)
+{
+    pdl_entry();
+    pdl_sync_small();
+    extern __shared__ float route_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= T) return;
+    float *sc = route_smem + (size_t)warp * (2 * E + n_groups), *ch = sc + E, *gs = ch + E;
+    float m = -INFINITY;
+    for (int e = lane; e < E; e += 32) {
+        float v = 0.f;
+        for (int s = 0; s < splits; s++) v += zs[((size_t)s * T + t) * E + e];
+        sc[e] = v;
+        m = fmaxf(m, v);
+    }
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float p = expf(sc[e] - m); sc[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) {
+        const float p = sc[e] * inv;
+        sc[e] = p;
+        ch[e] = correction ? p + load_any(correction, corr_dt, e) : p;
+    }
+    __syncwarp();
+    if (n_groups > 1 && keep < n_groups) {
+        const int per = E / n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float b = -INFINITY;
+            for (int i = 0; i < per; i++) b = fmaxf(b, ch[g * per + i]);
+            gs[g] = b;
+        }
+        __syncwarp();
+        // a group is kept when fewer than `keep` groups come before it in the order (score descending, index ascending)
+        for (int g = lane; g < n_groups; g += 32) {
+            const float mine = gs[g];
+            int before = 0;
+            for (int o = 0; o < n_groups; o++) before += (gs[o] > mine || (gs[o] == mine && o < g)) ? 1 : 0;
+            if (before >= keep)
+                for (int i = 0; i < per; i++) ch[g * per + i] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    for (int j = 0; j < top; j++) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = ch[e];
+            if (v > best || (v == best && e < bi && v > -INFINITY)) { best = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (bi == 0x7fffffff) bi = 0;                 // (nothing left to choose from)
+        if (lane == 0) {
+            ids[(size_t)t * top + j] = bi;
+            weights[(size_t)t * top + j] = sc[bi] * scale;
+            ch[bi] = -INFINITY;
+        }
+        __syncwarp();
     }
 }
 
@@ -107,6 +193,8 @@ moe_gemm_kernel(const TA *__restrict__ a, const TW *__restrict__ w, void *out, i
                 const int32_t *order, int src_div, int scatter, const int32_t *tile_expert, const int32_t *tile_p0,
                 const int32_t *tile_n, const int32_t *n_tiles)
 {
+    const int glu = act >> 8;          // HFB_ACT_GLU set: see the epilogue
+    act &= 255;
     pdl_sync();
     const int ti = blockIdx.y;
     if (ti >= *n_tiles) return;
@@ -170,12 +258,11 @@ moe_gemm_kernel(const TA *__restrict__ a, const TW *__restrict__ w, void *out, i
         for (int j = 0; j < 4; j++) {
             const int gn = n0 + tx * 4 + j;
             if (gn >= N) continue;
-            float v = acc[i][j];
-            if (act == HFB_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
-            else if (act == HFB_ACT_RELU) v = fmaxf(v, 0.f);
-            else if (act == HFB_ACT_SILU) v = v / (1.0f + expf(-v));
-            else if (act == HFB_ACT_GELU_TANH) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
-            store_any(out, out_dt, (size_t)dst * N + gn, v);
+            if (glu) {              // rows of w alternate gate, up: features (2f, 2f + 1) give out[f] = act(gate) * up
+                if (!(j & 1)) store_any(out, out_dt, (size_t)dst * (N / 2) + gn / 2, moe_act(acc[i][j], act) * acc[i][j + 1]);
+                continue;
+            }
+            store_any(out, out_dt, (size_t)dst * N + gn, moe_act(acc[i][j], act));
         }
     }
 }
@@ -222,6 +309,8 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
                     int N, int K, const int32_t *order, int src_div, int scatter, const int32_t *tile_expert,
                     const int32_t *tile_p0, const int32_t *tile_n, const int32_t *n_tiles)
 {
+    const int glu = act >> 8;          // HFB_ACT_GLU set: see the epilogue
+    act &= 255;
     pdl_sync();
     const int ti = blockIdx.y;
     if (ti >= *n_tiles) return;
@@ -322,12 +411,11 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *__
                 for (int j = 0; j < 2; j++) {
                     const int gn = n0 + 64 * wn + nt * 8 + 2 * t + j;
                     if (gn >= n_end) continue;
-                    float v = acc[m][nt][2 * half + j];
-                    if (act == HFB_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
-                    else if (act == HFB_ACT_RELU) v = fmaxf(v, 0.f);
-                    else if (act == HFB_ACT_SILU) v = v / (1.0f + expf(-v));
-                    else if (act == HFB_ACT_GELU_TANH) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
-                    store_any(out, out_dt, (size_t)dst * N + gn, v);
+                    if (glu) {
+                        if (j == 0) store_any(out, out_dt, (size_t)dst * (N / 2) + gn / 2, moe_act(acc[m][nt][2 * half], act) * acc[m][nt][2 * half + 1]);
+                        continue;
+                    }
+                    store_any(out, out_dt, (size_t)dst * N + gn, moe_act(acc[m][nt][2 * half + j], act));
                 }
             }
         }
@@ -346,6 +434,8 @@ moe_gemm_small_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *
                       int N, int K, const int32_t *order, int src_div, int scatter, const int32_t *tile_expert,
                       const int32_t *tile_p0, const int32_t *tile_n, const int32_t *n_tiles)
 {
+    const int glu = act >> 8;          // HFB_ACT_GLU set: see the epilogue
+    act &= 255;
     pdl_sync();
     const int ti = blockIdx.y;
     if (ti >= *n_tiles) return;
@@ -425,12 +515,11 @@ moe_gemm_small_kernel(const __nv_bfloat16 *__restrict__ a, const __nv_bfloat16 *
             for (int j = 0; j < 2; j++) {
                 const int gn = n0 + 16 * warp + nt * 8 + 2 * t + j;
                 if (gn >= N) continue;
-                float v = acc[nt][2 * half + j];
-                if (act == HFB_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
-                else if (act == HFB_ACT_RELU) v = fmaxf(v, 0.f);
-                else if (act == HFB_ACT_SILU) v = v / (1.0f + expf(-v));
-                else if (act == HFB_ACT_GELU_TANH) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
-                store_any(out, out_dt, (size_t)dst * N + gn, v);
+                if (glu) {
+                    if (j == 0) store_any(out, out_dt, (size_t)dst * (N / 2) + gn / 2, moe_act(acc[nt][2 * half], act) * acc[nt][2 * half + 1]);
+                    continue;
+                }
+                store_any(out, out_dt, (size_t)dst * N + gn, moe_act(acc[nt][2 * half + j], act));
             }
         }
     }
@@ -473,6 +562,20 @@ extern "C" int hfb_moe_topk(const float *z, int splits, const void *bias, int bi
     return check_pdl_launch(g_launch_err, "moe_topk");
 }
 
+extern "C" int hfb_moe_route_softmax(const float *z, int splits, const void *correction, int corr_dt, int T, int E, int top,
+                                     int n_groups, int keep, float scale, int32_t *ids, float *weights, hfb_stream s)
+{
+    if (T <= 0) return HFB_OK;
+    if (E <= 0 || top <= 0 || top > E || splits < 1 || (correction && !valid_dt(corr_dt)) || n_groups < 1 || E % n_groups ||
+        keep < 1 || keep > n_groups || keep * (E / n_groups) < top)
+        return fail(HFB_EINVAL, "moe_route_softmax: bad arguments (outputs=%d top=%d groups=%d keep=%d)", E, top, n_groups, keep);
+    const size_t smem = (size_t)ROUTE_WARPS * (2 * E + n_groups) * sizeof(float);
+    if (smem > 48 * 1024) return fail(HFB_ENOTSUP, "moe_route_softmax: %d router outputs are more than the kernel takes", E);
+    g_launch_err = launch_pdl(moe_route_softmax_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, (cudaStream_t)s,
+                              z, splits, correction, corr_dt, T, E, top, n_groups, keep, scale, ids, weights);
+    return check_pdl_launch(g_launch_err, "moe_route_softmax");
+}
+
 extern "C" int hfb_moe_max_tiles(int pairs, int E, int tile)
 {
     if (pairs <= 0 || E <= 0 || tile <= 0) return 0;
@@ -495,7 +598,8 @@ extern "C" int hfb_moe_gemm(const void *a, int a_dt, const void *w, int w_dt, vo
                             const int32_t *tile_n, const int32_t *n_tiles, int max_tiles, int tile, hfb_stream s)
 {
     if (max_tiles <= 0) return HFB_OK;
-    if (!valid_dt(a_dt) || !valid_dt(w_dt) || !valid_dt(out_dt) || N <= 0 || K <= 0 || tile < 1 || tile > MT || act < 0 || act > HFB_ACT_NONE)
+    if (!valid_dt(a_dt) || !valid_dt(w_dt) || !valid_dt(out_dt) || N <= 0 || K <= 0 || tile < 1 || tile > MT || act < 0 || (act & 255) > HFB_ACT_NONE ||
+        (act >> 8) > 1 || ((act >> 8) && (N & 1)))
         return fail(HFB_EINVAL, "moe_gemm: bad arguments (N=%d K=%d tile=%d)", N, K, tile);
     if (max_tiles > 65535) return fail(HFB_ENOTSUP, "moe_gemm: %d tiles exceed the grid", max_tiles);
     const dim3 grid((N + GT - 1) / GT, max_tiles);

@@ -1,0 +1,317 @@
+// Mixers that carry a matrix of fixed size per request and head instead of keys and values per token: the gated
+// linear recurrence
+//     S <- diag(a_t) S + k_t u_t^T,   o_t = S^T q_t,   u_t = v_t                         (gated linear attention)
+//                                                     u_t = beta_t (v_t - (diag(a_t) S)^T k_t)   (gated delta rule)
+// with S [d, dv] per head (the decay a_t acts on the rows, which belong to key channels), and what stands around it:
+// the decays from their logits, the short causal convolution over time with its carried inputs, unit-length queries
+// and keys, and the heads' root-mean-square norm with its gate.  The state, the decays and every sum are float32; the
+// state of a request lives in its slot between steps, so a step continues exactly where the last one stopped and a
+// token's result does not depend on how the request was cut into steps nor on what else a step holds.
+//
+// Layout of a head's state in a slot: [dv][d], a column of S (one value channel) contiguous.  Columns are independent
+// of each other in both forms of the recurrence, so the work is spread over (request, head, column) and only the walk
+// along a request's tokens is sequential.
+#include "common.cuh"
+
+static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
+
+namespace hfb {
+int *error_word();
+
+constexpr int CONV_MAX_TAPS = 16;
+constexpr int REC_WARPS = 4;
+constexpr int REC_MAX_D = 512;
+
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// a[t, h, i] = exp(-rate[h] * softplus(sign * (z[t, h, i] + bias[h, i]))), z the sum of `splits` planes [T, z_stride] read
+// from column z_col0 on.  sign = +1 with rate = exp(A_log): exp(-exp(A_log) softplus(z + dt_bias)); sign = -1 with rate
+// = 1 / tau: sigmoid(z + bias)^(1 / tau).
+__global__ void decay_kernel(const float *z, int splits, int z_stride, int z_col0, const void *bias, int bias_dt,
+                             const float *rate, float sign, float *out, int T, int H, int d)
+{
+    pdl_entry();
+    pdl_sync_small();
+    const size_t row = (size_t)H * d, total = (size_t)T * row, plane = (size_t)T * z_stride;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % row);
+        const float *zp = z + (i / row) * z_stride + z_col0 + c;
+        float v = 0.f;
+        for (int s = 0; s < splits; s++) v += zp[(size_t)s * plane];
+        if (bias) v += load_any(bias, bias_dt, c);
+        out[i] = expf(-rate[c / d] * softplus_f(sign * v));
+    }
+}
+
+// Short causal convolution over time, per channel, then silu; the heads of the first `n_unit` units are then brought
+// to unit length, x / sqrt(sum(x^2) + unit_eps), and those of the first `n_scaled` also multiplied by `scale`.  A row of
+// x is a list of units (heads): `n_a` units of `d_a` channels followed by `n_b` units of `d_b`.  One warp per (token,
+// unit).  Inputs before a request's first token of this step come from its slot, carried [taps - 1][C] oldest first
+// (zeros for a new request).  w [C, taps], the last column is the current token's.
+__global__ void __launch_bounds__(REC_WARPS * 32)
+short_conv_kernel(const float *x, int splits, const void *w, int w_dt, int taps, const float *carried, size_t slot_stride,
+                  const int32_t *token_seq, const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, float *out,
+                  int T, int n_a, int d_a, int n_b, int d_b, int n_unit, int n_scaled, float scale, float unit_eps, int *err)
+{
+    pdl_entry();
+    pdl_sync_small();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x, u = blockIdx.y * REC_WARPS + warp;
+    if (u >= n_a + n_b) return;
+    const int C = n_a * d_a + n_b * d_b;
+    const int col0 = u < n_a ? u * d_a : n_a * d_a + (u - n_a) * d_b;
+    const int n = u < n_a ? d_a : d_b;
+    const int seq = token_seq[t];
+    const int t0 = cu_tokens[seq];
+    const int slot = seq_slots[seq];
+    if (slot < 0 || slot >= n_slots) { if (lane == 0) atomicOr(err, HFB_ERR_SLOT); return; }
+    const float *old = carried + (size_t)slot * slot_stride;
+    const size_t plane = (size_t)T * C;
+    const int K = taps - 1;
+    float ss = 0.f;
+    for (int c = lane; c < n; c += 32) {
+        const int ch = col0 + c;
+        float acc = 0.f;
+        for (int i = 0; i < taps; i++) {
+            const int tt = t - K + i;                        // the input i - K tokens back
+            float v = 0.f;
+            if (tt >= t0) {
+                for (int s = 0; s < splits; s++) v += x[(size_t)s * plane + (size_t)tt * C + ch];
+            } else {
+                v = old[(size_t)(tt - t0 + K) * C + ch];
+            }
+            acc = fmaf(load_any(w, w_dt, (size_t)ch * taps + i), v, acc);
+        }
+        const float y = acc * sigmoid_f(acc);
+        out[(size_t)t * C + ch] = y;
+        ss = fmaf(y, y, ss);
+    }
+    if (u < n_unit) {
+        ss = warp_sum(ss);
+        float r = 1.0f / sqrtf(ss + unit_eps);
+        if (u < n_scaled) r *= scale;
+        __syncwarp();
+        for (int c = lane; c < n; c += 32) out[(size_t)t * C + col0 + c] *= r;
+    }
+}
+
+// The convolution's carried inputs after a step: the last taps - 1 inputs of each request, from this step's rows and,
+// where the step brought fewer, from what was carried before.  One thread per (request, channel) reads all it needs
+// before it writes.
+__global__ void conv_carry_kernel(const float *x, int splits, int taps, float *carried, size_t slot_stride,
+                                  const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, int S, int T, int C)
+{
+    pdl_entry();
+    pdl_sync_small();
+    const int K = taps - 1;
+    const size_t plane = (size_t)T * C;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)S * C; i += (size_t)gridDim.x * blockDim.x) {
+        const int seq = (int)(i / C), ch = (int)(i % C);
+        const int slot = seq_slots[seq];
+        if (slot < 0 || slot >= n_slots) continue;
+        const int t0 = cu_tokens[seq], n = cu_tokens[seq + 1] - t0;
+        float *st = carried + (size_t)slot * slot_stride;
+        float keep[CONV_MAX_TAPS];
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; j++) {
+            if (j < K) {
+                const int rel = n - K + j;                   // relative to the step's first token of the request
+                float v = 0.f;
+                if (rel >= 0) { for (int s = 0; s < splits; s++) v += x[(size_t)s * plane + (size_t)(t0 + rel) * C + ch]; }
+                else v = st[(size_t)(rel + K) * C + ch];
+                keep[j] = v;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; j++)
+            if (j < K) st[(size_t)j * C + ch] = keep[j];
+    }
+}
+
+// The recurrence.  Block = (request, head, slice of value channels); L lanes share a column of S, each holding R of its
+// d entries in registers (entry i of the column sits in lane i / R).  q and k rows are [Hq heads of d] (head h reads head
+// h / (H / Hq)), a (the decays) [H heads of d], v and o [H heads of dv]; every row pointer comes with its own stride so
+// that the operands may be slices of wider product outputs.  beta_logit [T, beta_stride]: u = sigmoid(beta_logit) (v -
+// S^T k); NULL: u = v.  The next token's operands are fetched while the current one is worked on.
+template <int R, int L>
+__global__ void __launch_bounds__(256)
+linear_scan_kernel(const float *q, int q_stride, const float *k, int k_stride, const float *v, int v_stride,
+                   const float *a, int a_stride, const float *beta_logit, int beta_stride, float q_scale, float *state,
+                   size_t slot_stride, const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, float *o,
+                   int o_stride, int H, int Hq, int d, int dv, int *err)
+{
+    pdl_entry();
+    pdl_sync_small();
+    constexpr int COLS = 256 / L;
+    const int seq = blockIdx.x, h = blockIdx.y;
+    const int col = blockIdx.z * COLS + threadIdx.x / L, part = threadIdx.x % L;
+    const int slot = seq_slots[seq];
+    if (slot < 0 || slot >= n_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
+    const int t0 = cu_tokens[seq], t1 = cu_tokens[seq + 1];
+    const bool live = col < dv;                                  // (lanes beyond the last column follow along on column 0)
+    const int cj = live ? col : 0;
+    const int hq = h / (H / Hq);
+    const int i0 = part * R;
+    float *sp = state + (size_t)slot * slot_stride + ((size_t)h * dv + cj) * d + i0;
+    float S[R], qa[R], ka[R], aa[R], qn[R], kn[R], an[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) S[r] = (i0 + r < d) ? sp[r] : 0.f;
+    float vn = 0.f, bn = 0.f;
+    auto fetch = [&](int t) {
+        const float *qp = q + (size_t)t * q_stride + hq * d + i0, *kp = k + (size_t)t * k_stride + hq * d + i0;
+        const float *ap = a + (size_t)t * a_stride + h * d + i0;
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const bool in = i0 + r < d;
+            qn[r] = in ? qp[r] : 0.f;
+            kn[r] = in ? kp[r] : 0.f;
+            an[r] = in ? ap[r] : 0.f;
+        }
+        vn = v[(size_t)t * v_stride + h * dv + cj];
+        bn = beta_logit ? beta_logit[(size_t)t * beta_stride + h] : 0.f;
+    };
+    if (t0 < t1) fetch(t0);
+    for (int t = t0; t < t1; t++) {
+#pragma unroll
+        for (int r = 0; r < R; r++) { qa[r] = qn[r]; ka[r] = kn[r]; aa[r] = an[r]; }
+        const float vt = vn, bt = bn;
+        if (t + 1 < t1) fetch(t + 1);
+        float u = vt;
+        if (beta_logit) {
+            float dot = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; r++) { S[r] *= aa[r]; dot = fmaf(S[r], ka[r], dot); }
+#pragma unroll
+            for (int m = L / 2; m > 0; m >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
+            u = sigmoid_f(bt) * (vt - dot);
+#pragma unroll
+            for (int r = 0; r < R; r++) S[r] = fmaf(ka[r], u, S[r]);
+        } else {
+#pragma unroll
+            for (int r = 0; r < R; r++) S[r] = fmaf(aa[r], S[r], ka[r] * u);
+        }
+        float acc = 0.f;
+#pragma unroll
+        for (int r = 0; r < R; r++) acc = fmaf(S[r], qa[r], acc);
+#pragma unroll
+        for (int m = L / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+        if (live && part == 0) o[(size_t)t * o_stride + h * dv + col] = acc * q_scale;
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < R; r++)
+            if (i0 + r < d) sp[r] = S[r];
+    }
+}
+
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w * gate(g[t, h, :]); gate 0: silu, 1: sigmoid.  g is the sum of
+// `g_splits` planes [T, g_stride] (float32) read from column g_col0 on.  One warp per (token, head).
+template <typename TO>
+__global__ void __launch_bounds__(REC_WARPS * 32)
+gate_norm_kernel(const float *o, const void *w, int w_dt, float eps, const float *g, int g_splits, int g_stride, int g_col0,
+                 int gate, TO *out, int T, int H, int dv)
+{
+    pdl_entry();
+    pdl_sync_small();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x, h = blockIdx.y * REC_WARPS + warp;
+    if (h >= H) return;
+    const float *x = o + ((size_t)t * H + h) * dv;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) ss = fmaf(x[c], x[c], ss);
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)dv + eps);
+    const size_t plane = (size_t)T * g_stride;
+    for (int c = lane; c < dv; c += 32) {
+        float z = 0.f;
+        const float *gp = g + (size_t)t * g_stride + g_col0 + h * dv + c;
+        for (int s = 0; s < g_splits; s++) z += gp[(size_t)s * plane];
+        const float gv = gate == 0 ? z * sigmoid_f(z) : sigmoid_f(z);
+        out[((size_t)t * H + h) * dv + c] = from_f32<TO>(x[c] * r * load_any(w, w_dt, c) * gv);
+    }
+}
+
+static unsigned rec_blocks(size_t total)
+{
+    size_t b = (total + 255) / 256;
+    return (unsigned)(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
+}
+
+}  // namespace hfb
+
+using namespace hfb;
+
+extern "C" int hfb_decay(const float *z, int splits, int z_stride, int z_col0, const void *bias, int bias_dt, const float *rate,
+                         float sign, float *out, int T, int H, int d, hfb_stream s)
+{
+    if (T <= 0) return HFB_OK;
+    if (!z || !rate || !out || splits < 1 || H <= 0 || d <= 0 || (bias && !valid_dt(bias_dt)) || z_col0 < 0 || z_col0 + H * d > z_stride)
+        return fail(HFB_EINVAL, "decay: bad arguments (H=%d d=%d)", H, d);
+    g_launch_err = launch_pdl(decay_kernel, dim3(rec_blocks((size_t)T * H * d)), dim3(256), 0, (cudaStream_t)s, z, splits, z_stride, z_col0,
+                              bias, bias_dt, rate, sign, out, T, H, d);
+    return check_pdl_launch(g_launch_err, "decay");
+}
+
+extern "C" int hfb_short_conv(const float *x, int splits, const void *w, int w_dt, int taps, float *carried, int64_t slot_stride,
+                              const int32_t *token_seq, const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, int S,
+                              float *out, int T, int n_a, int d_a, int n_b, int d_b, int n_unit, int n_scaled, float scale,
+                              float unit_eps, hfb_stream s)
+{
+    if (T <= 0) return HFB_OK;
+    if (!x || !w || !carried || !out || !valid_dt(w_dt) || splits < 1 || taps < 1 || n_a < 0 || n_b < 0 || n_a + n_b < 1 ||
+        d_a <= 0 || d_b <= 0 || S < 1)
+        return fail(HFB_EINVAL, "short_conv: bad arguments (taps=%d)", taps);
+    if (taps > CONV_MAX_TAPS) return fail(HFB_ENOTSUP, "short_conv: %d taps exceed %d", taps, CONV_MAX_TAPS);
+    const int unit_blocks = (n_a + n_b + REC_WARPS - 1) / REC_WARPS;
+    if (unit_blocks > 65535) return fail(HFB_ENOTSUP, "short_conv: %d heads exceed the grid limit", n_a + n_b);
+    g_launch_err = launch_pdl(short_conv_kernel, dim3(T, unit_blocks), dim3(REC_WARPS * 32), 0, (cudaStream_t)s, x, splits, w, w_dt, taps,
+                              (const float *)carried, (size_t)slot_stride, token_seq, cu_tokens, seq_slots, n_slots, out, T, n_a, d_a,
+                              n_b, d_b, n_unit, n_scaled, scale, unit_eps, error_word());
+    int rc = check_pdl_launch(g_launch_err, "short_conv");
+    if (rc != HFB_OK || taps == 1) return rc;
+    const int C = n_a * d_a + n_b * d_b;
+    g_launch_err = launch_pdl(conv_carry_kernel, dim3(rec_blocks((size_t)S * C)), dim3(256), 0, (cudaStream_t)s, x, splits, taps, carried,
+                              (size_t)slot_stride, cu_tokens, seq_slots, n_slots, S, T, C);
+    return check_pdl_launch(g_launch_err, "conv_carry");
+}
+
+extern "C" int hfb_linear_scan(const float *q, int q_stride, const float *k, int k_stride, const float *v, int v_stride,
+                               const float *a, int a_stride, const float *beta_logit, int beta_stride, float q_scale,
+                               float *state, int64_t slot_stride, const int32_t *cu_tokens, const int32_t *seq_slots,
+                               int n_slots, int S, float *o, int o_stride, int H, int Hq, int d, int dv, hfb_stream s)
+{
+    if (S <= 0) return HFB_OK;
+    if (!q || !k || !v || !a || !state || !o || H <= 0 || Hq <= 0 || H % Hq || d <= 0 || dv <= 0)
+        return fail(HFB_EINVAL, "linear_scan: bad arguments (H=%d Hq=%d d=%d dv=%d)", H, Hq, d, dv);
+    if (d > REC_MAX_D) return fail(HFB_ENOTSUP, "linear_scan: key heads above %d are not supported", REC_MAX_D);
+    if (H > 65535) return fail(HFB_ENOTSUP, "linear_scan: %d heads exceed the grid limit", H);
+#define HFB_SCAN(R, L) \
+    g_launch_err = launch_pdl(linear_scan_kernel<R, L>, dim3(S, H, (dv + 256 / L - 1) / (256 / L)), dim3(256), 0, (cudaStream_t)s, q, q_stride, \
+        k, k_stride, v, v_stride, a, a_stride, beta_logit, beta_stride, q_scale, state, (size_t)slot_stride, cu_tokens, seq_slots, n_slots, \
+        o, o_stride, H, Hq, d, dv, error_word())
+    if (d <= 32) HFB_SCAN(4, 8);
+    else if (d <= 64) HFB_SCAN(8, 8);
+    else if (d <= 128) HFB_SCAN(16, 8);
+    else if (d <= 256) HFB_SCAN(16, 16);
+    else HFB_SCAN(16, 32);
+#undef HFB_SCAN
+    return check_pdl_launch(g_launch_err, "linear_scan");
+}
+
+extern "C" int hfb_gate_norm(const float *o, const void *w, int w_dt, float eps, const float *g, int g_splits, int g_stride,
+                             int g_col0, int gate, void *out, int out_dt, int T, int H, int dv, hfb_stream s)
+{
+    if (T <= 0) return HFB_OK;
+    if (!o || !w || !g || !out || !valid_dt(w_dt) || !valid_dt(out_dt) || g_splits < 1 || H <= 0 || dv <= 0 || (gate != 0 && gate != 1))
+        return fail(HFB_EINVAL, "gate_norm: bad arguments (H=%d dv=%d)", H, dv);
+    const int hb = (H + REC_WARPS - 1) / REC_WARPS;
+    if (hb > 65535) return fail(HFB_ENOTSUP, "gate_norm: %d heads exceed the grid limit", H);
+    if (out_dt == HFB_F32)
+        g_launch_err = launch_pdl(gate_norm_kernel<float>, dim3(T, hb), dim3(REC_WARPS * 32), 0, (cudaStream_t)s, o, w, w_dt, eps, g, g_splits,
+                                  g_stride, g_col0, gate, (float *)out, T, H, dv);
+    else
+        g_launch_err = launch_pdl(gate_norm_kernel<__nv_bfloat16>, dim3(T, hb), dim3(REC_WARPS * 32), 0, (cudaStream_t)s, o, w, w_dt, eps, g,
+                                  g_splits, g_stride, g_col0, gate, (__nv_bfloat16 *)out, T, H, dv);
+    return check_pdl_launch(g_launch_err, "gate_norm");
+}

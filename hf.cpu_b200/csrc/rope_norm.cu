@@ -6,7 +6,8 @@
 // slot.  A layer whose values are mixed with those of an earlier layer (v <- (1 - lambda) v + lambda v_first, v_first the
 // same token's values in the first such layer) does that here, before the store, so that the cache holds the mixed
 // values; the first such layer leaves its own values behind for the others.  Everything between the float32 sums and the
-// stores is float32.
+// stores is float32.  pairing 1 rotates the pairs (2i, 2i + 1) instead.  dv = 0: the row has no value heads (the layer's
+// values are its keys) and nothing is written to v_cache.
 #include "common.cuh"
 
 static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
@@ -33,14 +34,14 @@ __global__ void __launch_bounds__(RN_WARPS * 32)
 rope_norm_kv_kernel(const float *src, int splits, const void *bias, int bias_dt, const float *cos_sin, int n_rot,
                     int n_positions, const int32_t *positions, const int32_t *slots, TO *q_out, TO *k_cache, TO *v_cache,
                     long long cache_slots, int T, int H, int G, int d, int dv, int norm, float eps, const float *q_w,
-                    const float *k_w, float *v_first, int v_mode, float v_lambda, int *err)
+                    const float *k_w, float *v_first, int v_mode, float v_lambda, int pairing, int *err)
 {
     pdl_entry();
     pdl_sync_small();
     __shared__ __align__(16) float buf[RN_WARPS][RN_MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // a token per blockIdx.x, four of its units per blockIdx.y (no division to find them)
-    const int units = H + 2 * G;
+    const int units = H + (dv > 0 ? 2 : 1) * G;
     const int t = blockIdx.x, u = blockIdx.y * RN_WARPS + warp;
     if (u >= units) return;
     const int C = H * d + G * d + G * dv;
@@ -102,9 +103,10 @@ rope_norm_kv_kernel(const float *src, int splits, const void *bias, int bias_dt,
         const float *cs = cos_sin + (size_t)pos * half * 2;
         for (int i = lane; i < half; i += 32) {
             float lo, hi;
-            rope_pair(x[i], x[i + half], cs[2 * i], cs[2 * i + 1], lo, hi);
-            x[i] = lo;
-            x[i + half] = hi;
+            const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
+            rope_pair(x[ia], x[ib], cs[2 * i], cs[2 * i + 1], lo, hi);
+            x[ia] = lo;
+            x[ib] = hi;
         }
         __syncwarp();
     }
@@ -136,25 +138,25 @@ extern "C" int hfb_rope_norm_kv_write(const float *src, int splits, const void *
                                       int n_rot, int n_positions, const int32_t *positions, const int32_t *slots,
                                       void *q_out, void *k_cache, void *v_cache, int out_dt, int64_t cache_slots, int T,
                                       int H, int G, int d, int dv, int norm, float eps, const float *q_w, const float *k_w,
-                                      float *v_first, int v_mode, float v_lambda, hfb_stream s)
+                                      float *v_first, int v_mode, float v_lambda, int pairing, hfb_stream s)
 {
     if (T <= 0) return HFB_OK;
-    if (!valid_dt(out_dt) || (bias && !valid_dt(bias_dt)) || splits < 1 || H <= 0 || G < 0 || d <= 0 || dv <= 0 ||
+    if (!valid_dt(out_dt) || (bias && !valid_dt(bias_dt)) || splits < 1 || H <= 0 || G < 0 || d <= 0 || dv < 0 ||
         n_rot < 0 || n_rot > d || (n_rot & 1))
         return fail(HFB_EINVAL, "rope_norm_kv_write: bad arguments (H=%d G=%d d=%d dv=%d n_rot=%d)", H, G, d, dv, n_rot);
     if (d > RN_MAX_D || dv > RN_MAX_D) return fail(HFB_ENOTSUP, "rope_norm_kv_write: head sizes above %d are not supported", RN_MAX_D);
     if (n_rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "rope_norm_kv_write: rotation needs a table and positions");
     if (v_mode < 0 || v_mode > 2 || (v_mode && (!v_first || G <= 0))) return fail(HFB_EINVAL, "rope_norm_kv_write: value mixing needs the first layer's values");
-    if (G > 0 && slots && (!k_cache || !v_cache)) return fail(HFB_EINVAL, "rope_norm_kv_write: keys and values need a cache");
-    const int unit_blocks = (H + 2 * G + RN_WARPS - 1) / RN_WARPS;
+    if (G > 0 && slots && (!k_cache || (dv > 0 && !v_cache))) return fail(HFB_EINVAL, "rope_norm_kv_write: keys and values need a cache");
+    const int unit_blocks = (H + (dv > 0 ? 2 : 1) * G + RN_WARPS - 1) / RN_WARPS;
     if (unit_blocks > 65535) return fail(HFB_ENOTSUP, "rope_norm_kv_write: %d heads exceed the grid limit", H + 2 * G);
     const dim3 blocks(T, unit_blocks);
     if (out_dt == HFB_F32)
         g_launch_err = launch_pdl(rope_norm_kv_kernel<float>, blocks, dim3(RN_WARPS * 32), 0, (cudaStream_t)s, src, splits, bias, bias_dt, cos_sin, n_rot,
-            n_positions, positions, slots, (float *)q_out, (float *)k_cache, (float *)v_cache, (long long)cache_slots, T, H, G, d, dv, norm, eps, q_w, k_w, v_first, v_mode, v_lambda, error_word());
+            n_positions, positions, slots, (float *)q_out, (float *)k_cache, (float *)v_cache, (long long)cache_slots, T, H, G, d, dv, norm, eps, q_w, k_w, v_first, v_mode, v_lambda, pairing, error_word());
     else
         g_launch_err = launch_pdl(rope_norm_kv_kernel<__nv_bfloat16>, blocks, dim3(RN_WARPS * 32), 0, (cudaStream_t)s, src, splits, bias, bias_dt, cos_sin, n_rot,
             n_positions, positions, slots, (__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (long long)cache_slots, T, H, G, d, dv, norm, eps,
-            q_w, k_w, v_first, v_mode, v_lambda, error_word());
+            q_w, k_w, v_first, v_mode, v_lambda, pairing, error_word());
     return check_pdl_launch(g_launch_err, "rope_norm_kv_write");
 }

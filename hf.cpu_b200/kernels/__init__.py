@@ -192,25 +192,35 @@ def tiled_attention_takes(dtype, head_dim: int, block_size: int) -> bool:
             and getattr(b, "attention", "plain") == "fast")
 
 
-def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None, dv=None, values_in_keys=False) -> None:
+def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None, dv=None, values_in_keys=False,
+                    sinks=None, zero_sink=False, slopes=None) -> None:
     """``window``: a :func:`mask_code`.  ``tiles``: the device arrays of :func:`attention_step_arrays` for this step
     (without them only the plain kernel runs).  ``dv``: the size of a value head where it is not ``d``; ``out`` is then
-    [T, H * dv].  ``values_in_keys``: there is no array of values, a value is the first ``dv`` elements of its key."""
+    [T, H * dv].  ``values_in_keys``: there is no array of values, a value is the first ``dv`` elements of its key.
+    ``sinks`` (float32 [H]): a score per head that joins the softmax's denominator once and has no value; ``zero_sink``:
+    such a score of 0 for every head (one is added to the denominator).  ``slopes`` (float32 [H]): slope * (query
+    position - key position) is taken off every score."""
     dv = d if dv is None else int(dv)
+    extra = {}
+    if sinks is not None or zero_sink or slopes is not None:
+        _need(sinks is None or (sinks.shape == (H,) and sinks.dtype == torch.float32), "attention: sinks are float32 [H]")
+        _need(slopes is None or (slopes.shape == (H,) and slopes.dtype == torch.float32), "attention: slopes are float32 [H]")
+        _need(not (zero_sink and sinks is not None), "attention: a learned sink or a sink of zero, not both")
+        extra = {"sinks": sinks, "zero_sink": bool(zero_sink), "slopes": slopes}
     if values_in_keys:
         _need(0 < dv <= d <= MAX_LATENT_ROW and v_cache is None, "attention: values inside keys need dv <= d <= %d" % MAX_LATENT_ROW)
         _need(q.shape[1] == H * d and out.shape == (q.shape[0], H * dv) and k_cache.shape[2:] == (G, d), "attention: shape mismatch")
         _need(q.dtype == k_cache.dtype == out.dtype, "attention: element types differ")
-        backend().paged_attention(q, k_cache, None, meta, ctx, H, G, d, int(window), float(scale), out, tiles or {}, dv=dv)
+        backend().paged_attention(q, k_cache, None, meta, ctx, H, G, d, int(window), float(scale), out, tiles or {}, dv=dv, **extra)
         return
     _need(0 < d <= MAX_HEAD_DIM and 0 < dv <= MAX_HEAD_DIM, "attention: head sizes must be 1..%d" % MAX_HEAD_DIM)
     _need(q.shape[1] == H * d and out.shape == (q.shape[0], H * dv), "attention: shape mismatch")
     _need(k_cache.shape[2:] == (G, d) and v_cache.shape[2:] == (G, dv), "attention: cache geometry mismatch")
     _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype, "attention: element types differ")
     if dv == d:
-        backend().paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, int(window), float(scale), out, tiles or {})
+        backend().paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, int(window), float(scale), out, tiles or {}, **extra)
     else:
-        backend().paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, int(window), float(scale), out, tiles or {}, dv=dv)
+        backend().paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, int(window), float(scale), out, tiles or {}, dv=dv, **extra)
 
 
 def swiglu(gu: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
@@ -246,6 +256,7 @@ def linear_rope_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out,
 
 
 ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "relu2": 3, "none": 4}       # relu2: the square of relu
+ACT_GLU = 256               # added to an activation code: gated form of the grouped product
 MOE_TILE = 128              # places of one expert per tile of the grouped product ...
 MOE_TILE_FEW = 16           # ... and in steps of few tokens, whose blocks only stream weights: more, smaller tiles
 
@@ -321,9 +332,11 @@ def linear_dyt_residual(a, w, bias, y_buf, post, residual, nxt=None, out=None, m
 
 
 def linear_rope_norm_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d, dv,
-                        norm_eps, norm_weights=None, value_mix=None) -> None:
+                        norm_eps, norm_weights=None, value_mix=None, pairing: str = "half") -> None:
     """The q|k|v product and its tail for attention with unit-rms queries and keys: row = [H heads of d | G key heads
-    of d | G value heads of dv] (G = 0: the layer has no keys and values of its own); rotation of the first ``n_rot``
+    of d | G value heads of dv] (G = 0: the layer has no keys and values of its own; dv = 0: the row has no value heads,
+    the layer's values are its keys, and ``v_cache`` is None); ``pairing``: which dimensions turn together, "half"
+    (i, i + n_rot/2) or "interleaved" (2i, 2i + 1); rotation of the first ``n_rot``
     dimensions of query and key heads, then, unless ``norm_eps`` is None, x / sqrt(mean(x^2) + eps) per head, times
     ``norm_weights`` = (q weight, k weight), float32 [d] each, where the norm has weights; queries to ``q_out``, keys
     and values to the cache at ``slots``.  ``value_mix`` = (first [T, G * dv] float32, mode, lambda): mode 1 leaves the
@@ -338,10 +351,13 @@ def linear_rope_norm_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q
     C = H * d + G * (d + dv)
     _need(w.shape[0] == C and q_out.shape == (a.shape[0], H * d) and a.shape[1] == w.shape[1], "linear_rope_norm_kv: shape mismatch")
     _need(qkv_buf.shape == (a.shape[0], C) and qkv_buf.dtype == torch.float32, "linear_rope_norm_kv: scratch must be float32 [T, row]")
-    _need(0 < d <= MAX_HEAD_DIM and 0 < dv <= MAX_HEAD_DIM and n_rot % 2 == 0 and 0 <= n_rot <= d, "linear_rope_norm_kv: bad head sizes")
+    _need(0 < d <= MAX_HEAD_DIM and 0 <= dv <= MAX_HEAD_DIM and n_rot % 2 == 0 and 0 <= n_rot <= d, "linear_rope_norm_kv: bad head sizes")
+    _need(pairing in ("half", "interleaved"), "linear_rope_norm_kv: pairing is 'half' or 'interleaved'")
+    _need(dv > 0 or value_mix is None, "linear_rope_norm_kv: a row without values mixes none")
     if G:
-        _need(k_cache.shape[2:] == (G, d) and v_cache.shape[2:] == (G, dv) and k_cache.dtype == q_out.dtype == v_cache.dtype,
-              "linear_rope_norm_kv: cache geometry mismatch")
+        _need(k_cache.shape[2:] == (G, d) and k_cache.dtype == q_out.dtype, "linear_rope_norm_kv: cache geometry mismatch")
+        _need((v_cache is None) if dv == 0 else (v_cache.shape[2:] == (G, dv) and v_cache.dtype == q_out.dtype),
+              "linear_rope_norm_kv: cache geometry mismatch (values)")
     _need(n_rot == 0 or (cos_sin is not None and cos_sin.shape[1:] == (n_rot // 2, 2) and cos_sin.dtype == torch.float32),
           "linear_rope_norm_kv: cos/sin table must be float32 [positions, n_rot/2, 2]")
     extra = {}
@@ -349,6 +365,8 @@ def linear_rope_norm_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q
         extra["norm_weights"] = norm_weights
     if value_mix is not None:
         extra["value_mix"] = (value_mix[0], int(value_mix[1]), float(value_mix[2]))
+    if pairing != "half":
+        extra["pairing"] = pairing
     backend().linear_rope_norm_kv(a, w, bias, qkv_buf, cos_sin, int(n_rot), positions, slots, q_out, k_cache, v_cache,
                                   H, G, d, dv, None if norm_eps is None else float(norm_eps), **extra)
 
@@ -461,12 +479,15 @@ def moe_group(ids, experts: int, order, tile_expert, tile_p0, tile_n, n_tiles) -
     backend().moe_group(ids, int(experts), order, tile_expert, tile_p0, tile_n, n_tiles, moe_tile(pairs))
 
 
-def moe_gemm(a, w, out, act: str, order, src_div: int, scatter: bool, tile_expert, tile_p0, tile_n, n_tiles, pairs: int) -> None:
+def moe_gemm(a, w, out, act: str, order, src_div: int, scatter: bool, tile_expert, tile_p0, tile_n, n_tiles, pairs: int,
+             glu: bool = False) -> None:
     """Grouped product over the places of :func:`moe_group`: out[dst(p)] = act(a[src(p)] @ w[expert(p)].T) with
-    w [E, N, K]; src(p) = order[p] // src_div if src_div else p; dst(p) = order[p] if scatter else p."""
-    _need(w.dim() == 3 and a.shape[1] == w.shape[2] and out.shape[1] == w.shape[1], "moe_gemm: shape mismatch")
-    backend().moe_gemm(a, w, out, _act(act), order, int(src_div), bool(scatter), tile_expert, tile_p0, tile_n, n_tiles,
-                       moe_max_tiles(int(pairs), w.shape[0]), moe_tile(int(pairs)))
+    w [E, N, K]; src(p) = order[p] // src_div if src_div else p; dst(p) = order[p] if scatter else p.  ``glu``: the rows
+    of an expert's matrix alternate gate, up, and out [.., N / 2] = act(gate) * up."""
+    _need(w.dim() == 3 and a.shape[1] == w.shape[2], "moe_gemm: shape mismatch")
+    _need(out.shape[1] == (w.shape[1] // 2 if glu else w.shape[1]) and (not glu or w.shape[1] % 2 == 0), "moe_gemm: output width mismatch")
+    backend().moe_gemm(a, w, out, _act(act) | (ACT_GLU if glu else 0), order, int(src_div), bool(scatter), tile_expert, tile_p0,
+                       tile_n, n_tiles, moe_max_tiles(int(pairs), w.shape[0]), moe_tile(int(pairs)))
 
 
 def moe_combine(y, weights, out) -> None:
@@ -474,6 +495,152 @@ def moe_combine(y, weights, out) -> None:
     T, top = weights.shape
     _need(y.shape == (T * top, out.shape[1]) and out.shape[0] == T and out.dtype == torch.float32, "moe_combine: shape mismatch")
     backend().moe_combine(y, weights, out)
+
+
+def moe_route_softmax(h, w, correction, top: int, n_groups: int, keep: int, scale: float, ids, weights, logits) -> None:
+    """Router whose scores are a softmax over all of its outputs: s = softmax(h @ w.T) (float32); choice score = s +
+    ``correction`` (or s); the outputs form ``n_groups`` equal groups of neighbours, a group's score is its largest
+    choice score, and only outputs of the ``keep`` best groups can be chosen; ``ids`` = the ``top`` largest choice scores
+    (largest first, the lower index among equals), ``weights`` = s[ids] * scale, not renormalised."""
+    T, E = h.shape[0], w.shape[0]
+    _need(h.shape[1] == w.shape[1] and (correction is None or correction.shape == (E,)) and 1 <= top <= E, "moe_route_softmax: shape mismatch")
+    _need(n_groups >= 1 and E % n_groups == 0 and 1 <= keep <= n_groups and keep * (E // n_groups) >= top,
+          "moe_route_softmax: the kept groups must hold at least `top` outputs")
+    _need(ids.shape == (T, top) and ids.dtype == torch.int32 and weights.shape == (T, top) and weights.dtype == torch.float32,
+          "moe_route_softmax: ids int32 [T, top], weights float32 [T, top]")
+    _need(logits.shape == (T, E) and logits.dtype == torch.float32, "moe_route_softmax: logits float32 [T, outputs]")
+    backend().moe_route_softmax(h, w, correction, int(top), int(n_groups), int(keep), float(scale), ids, weights, logits)
+
+
+def product_sums(a, w, buf, finished: bool = False):
+    """float32 sums of ``a @ w.T`` for a kernel that goes on from them: returns (sums, splits), sums [splits, M, N].  Where
+    the tensor-core product is split over its inner dimension the pieces lie in the backend's one scratch area (valid
+    until the next product) and whoever reads them sums them in order; else, and always with ``finished``, the product
+    is in ``buf`` ([M, N] float32) and splits is 1."""
+    _need(a.shape[1] == w.shape[1] and buf.shape == (a.shape[0], w.shape[0]) and buf.dtype == torch.float32,
+          "product_sums: buf must be float32 [M, N]")
+    return backend().product_sums(a, w, buf, bool(finished))
+
+
+# ---- hyper-connections: the residual stream in S copies, x [T, S * E] float32 ------------------------------------
+def _hc_ok(x, S, E, what):
+    _need(x.dtype == torch.float32 and x.dim() == 2 and x.shape[1] == S * E and 1 <= S <= HC_MAX_STREAMS,
+          f"{what}: the stream is float32 [T, copies * width] with at most {HC_MAX_STREAMS} copies")
+
+
+HC_MAX_STREAMS = 8
+
+
+def hc_spread(emb, x, S: int) -> None:
+    """Every copy of the stream = emb [T, E] (float32)."""
+    _hc_ok(x, S, emb.shape[1], "hc_spread")
+    _need(emb.dtype == torch.float32 and emb.shape[0] == x.shape[0], "hc_spread: shape mismatch")
+    backend().hc_spread(emb, x, int(S))
+
+
+def hc_in_norm(x, S: int, in_w, rows, norm, out) -> None:
+    """out[m] = norm(sum_s in_w[s] * x[row(m), s]): ``in_w`` float32 [S] (None: the plain sum), ``rows`` int32 [M] (None:
+    every row), ``norm`` = the (alpha, w, b) of a Dynamic Tanh (None: no norm)."""
+    E = out.shape[1]
+    _hc_ok(x, S, E, "hc_in_norm")
+    _need(in_w is None or (in_w.shape == (S,) and in_w.dtype == torch.float32), "hc_in_norm: in_w is float32 [copies]")
+    _need(rows is None or (rows.dtype == torch.int32 and rows.shape[0] == out.shape[0]), "hc_in_norm: rows must be int32 [M]")
+    _need(rows is not None or out.shape[0] == x.shape[0], "hc_in_norm: row count mismatch")
+    if norm is not None:
+        _dyt_ok(norm, E, "hc_in_norm")
+    backend().hc_in_norm(x, int(S), in_w, rows, norm, out)
+
+
+def hc_update(x, S: int, sources, mix, scale, hc_mix, hc_out, next_in=None, next_norm=None, out=None) -> None:
+    """One sublayer's write-back.  y = scale .* (sum over ``sources`` of factor * (sum of the source's planes) + the
+    weighted sum of ``mix``); then every copy d of the stream from the old copies: x'[d] = sum_s hc_mix[s, d] x[s] +
+    hc_out[d] y; with ``out``, out = next_norm(sum_d next_in[d] x'[d]) from the same pass (next_in None: the plain sum;
+    next_norm None: no norm).  ``sources``: up to two (planes float32 [splits, T, E], splits, factor); ``mix`` = (rows
+    float32 [T * top, E], weights float32 [T, top], ids int32 [T, top] or None, n_real, h [T, E]): a choice whose id is at or
+    above n_real stands for the sublayer's input h itself.  ``scale``: [E] or None."""
+    T = x.shape[0]
+    E = x.shape[1] // S
+    _hc_ok(x, S, E, "hc_update")
+    _need(len(sources) <= 2 and (sources or mix is not None), "hc_update: one or two sources, or a mix")
+    for y, splits, _ in sources:
+        _need(y.dtype == torch.float32 and splits >= 1 and y.numel() >= splits * T * E, "hc_update: a source is float32 [splits, T, E]")
+    if mix is not None:
+        my, mw, mids, n_real, mh = mix
+        _need(mw.dim() == 2 and mw.shape[0] == T and my.shape == (T * mw.shape[1], E) and my.dtype == torch.float32
+              and mw.dtype == torch.float32, "hc_update: mix = (float32 [T * top, E], float32 [T, top], ...)")
+        _need(mids is None or (mids.shape == mw.shape and mids.dtype == torch.int32 and mh is not None and mh.shape == (T, E)),
+              "hc_update: ids int32 [T, top] come with the sublayer's input [T, E]")
+    _need(scale is None or scale.shape == (E,), "hc_update: scale is [E]")
+    _need(hc_mix.shape == (S, S) and hc_out.shape == (S,) and hc_mix.dtype == hc_out.dtype == torch.float32,
+          "hc_update: hc_mix float32 [S, S], hc_out float32 [S]")
+    _need(next_in is None or (next_in.shape == (S,) and next_in.dtype == torch.float32), "hc_update: next_in is float32 [S]")
+    _need(out is not None or (next_norm is None and next_in is None), "hc_update: the next norm needs an output")
+    if out is not None:
+        _need(out.shape == (T, E), "hc_update: output shape mismatch")
+        if next_norm is not None:
+            _dyt_ok(next_norm, E, "hc_update")
+    backend().hc_update(x, int(S), [(y, int(n), float(f)) for y, n, f in sources], mix, scale, hc_mix, hc_out, next_in, next_norm, out)
+
+
+# ---- recurrent mixers (float32 throughout) -----------------------------------------------------------------------
+CONV_MAX_TAPS = 16
+SCAN_MAX_HEAD = 512
+
+
+def decay(z, splits: int, bias, rate, sign: float, out, H: int, d: int, z_stride: int = 0, z_col0: int = 0) -> None:
+    """out[t, h, i] = exp(-rate[h] * softplus(sign * (z[t, h, i] + bias[h, i]))); z = the sum of ``splits`` float32 planes
+    [T, z_stride] read from column ``z_col0`` on (z_stride 0: planes [T, H * d]).  sign +1 with rate = exp(A): exp(-exp(A)
+    softplus(z + bias)); sign -1 with rate = 1 / tau: sigmoid(z + bias)^(1 / tau)."""
+    T = out.shape[0]
+    stride = int(z_stride) or H * d
+    _need(out.shape == (T, H * d) and out.dtype == torch.float32 and z.dtype == torch.float32 and z.numel() >= splits * T * stride
+          and z_col0 + H * d <= stride, "decay: z float32 [splits, T, stride], out float32 [T, H * d]")
+    _need(rate.shape == (H,) and rate.dtype == torch.float32 and (bias is None or bias.shape == (H * d,)), "decay: rate float32 [H], bias [H * d]")
+    backend().decay(z, int(splits), bias, rate, float(sign), out, int(H), int(d), stride, int(z_col0))
+
+
+def short_conv(x, splits: int, w, carried, ctx, out, n_a: int, d_a: int, n_b: int, d_b: int, n_unit: int = 0, n_scaled: int = 0,
+               scale: float = 1.0, unit_eps: float = 0.0) -> None:
+    """Causal convolution over time per channel, then silu: x = the sum of ``splits`` float32 planes [T, C]; w [C, taps],
+    the last column the current token's; ``carried`` [slots, taps - 1, C] float32 holds each request's last inputs
+    (zeros for a new request) and is brought up to date.  A row is ``n_a`` heads of ``d_a`` channels, then ``n_b`` of
+    ``d_b``: the first ``n_unit`` heads are then divided by sqrt(sum(x^2) + unit_eps), the first ``n_scaled`` of them also
+    times ``scale``.  A request's tokens continue from its slot ``ctx.seq_slots``."""
+    T, C = out.shape
+    taps = w.shape[1]
+    _need(C == n_a * d_a + n_b * d_b and w.shape[0] == C and 1 <= taps <= CONV_MAX_TAPS, "short_conv: channel count or taps mismatch")
+    _need(out.dtype == torch.float32 and x.dtype == torch.float32 and x.numel() >= splits * T * C, "short_conv: x float32 [splits, T, C]")
+    _need(carried.dtype == torch.float32 and carried.dim() == 3 and carried.shape[1:] == (max(taps - 1, 1), C)
+          and carried.stride()[1:] == (C, 1), "short_conv: carried is float32 [slots, taps - 1, C]")
+    _need(0 <= n_scaled <= n_unit <= n_a + n_b, "short_conv: scaled heads are among the unit heads")
+    backend().short_conv(x, int(splits), w, carried, ctx, out, int(n_a), int(d_a), int(n_b), int(d_b), int(n_unit), int(n_scaled),
+                         float(scale), float(unit_eps))
+
+
+def linear_scan(q, k, v, a, beta_logit, q_scale: float, state, ctx, o, H: int, Hq: int, d: int, dv: int) -> None:
+    """The gated linear recurrence per head, along each request's tokens from its slot's state: S <- diag(a) S + k u^T,
+    o = S^T q * q_scale, with u = v, or, with ``beta_logit`` [T, H], u = sigmoid(beta) (v - (diag(a) S)^T k).  q, k: rows
+    of ``Hq`` heads of ``d`` (head h reads head h // (H / Hq)); a: H heads of d; v, o: H heads of dv; all float32, each may
+    be a column slice of a wider array (row strides are taken from the tensors).  ``state`` float32 [slots, H, dv, d]."""
+    T = o.shape[0]
+    for t, n, what in ((q, Hq * d, "q"), (k, Hq * d, "k"), (v, H * dv, "v"), (a, H * d, "a"), (o, H * dv, "o")):
+        _need(t.dtype == torch.float32 and t.shape == (T, n) and t.stride(1) == 1, f"linear_scan: {what} is float32 [T, {n}] with unit column stride")
+    _need(beta_logit is None or (beta_logit.dtype == torch.float32 and beta_logit.shape == (T, H) and beta_logit.stride(1) == 1),
+          "linear_scan: beta_logit is float32 [T, H]")
+    _need(H % Hq == 0 and d <= SCAN_MAX_HEAD and state.dtype == torch.float32 and state.shape[1:] == (H, dv, d)
+          and state.stride()[1:] == (dv * d, d, 1),
+          "linear_scan: state is float32 [slots, H, dv, d]")
+    backend().linear_scan(q, k, v, a, beta_logit, float(q_scale), state, ctx, o, int(H), int(Hq), int(d), int(dv))
+
+
+def gate_norm(o, w, eps: float, g, g_splits: int, g_stride: int, g_col0: int, gate: str, out, H: int, dv: int) -> None:
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * w * gate(g[t, h]); o float32 [T, H * dv]; w [dv]; g = the sum of
+    ``g_splits`` float32 planes [T, g_stride] read from column ``g_col0`` on; gate "silu" or "sigmoid"."""
+    T = o.shape[0]
+    _need(o.dtype == torch.float32 and o.shape == (T, H * dv) and out.shape == (T, H * dv) and w.shape == (dv,), "gate_norm: shape mismatch")
+    _need(g.dtype == torch.float32 and g.numel() >= g_splits * T * g_stride and g_col0 + H * dv <= g_stride and gate in ("silu", "sigmoid"),
+          "gate_norm: g float32 [splits, T, stride]; gate silu or sigmoid")
+    backend().gate_norm(o, w, float(eps), g, int(g_splits), int(g_stride), int(g_col0), 0 if gate == "silu" else 1, out, int(H), int(dv))
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

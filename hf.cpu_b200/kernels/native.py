@@ -150,8 +150,11 @@ class NativeBackend:
                                                c_int64(cache_slots), c_int(T), c_int(H), c_int(G), c_int(d),
                                                self._stream()), "rope_kv_write")
 
-    def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tile_arrays, dv=None):
-        self._on_gpu(q, k_cache, v_cache, meta.block_table, ctx.token_seq, ctx.positions, out)
+    def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tile_arrays, dv=None, sinks=None,
+                        zero_sink=False, slopes=None):
+        self._on_gpu(q, k_cache, v_cache, meta.block_table, ctx.token_seq, ctx.positions, out, sinks, slopes)
+        if sinks is not None or zero_sink or slopes is not None:
+            tile_arrays = None                # a sink or a distance bias: the plain kernel has them
         T = q.shape[0]
         dv = d if dv is None else dv
         v_row = dv
@@ -247,7 +250,8 @@ class NativeBackend:
                                                  c_int(meta.max_blocks), _p(ctx.token_seq), _p(ctx.positions),
                                                  c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window),
                                                  c_float(scale), _p(out), c_int(T), c_int(H), c_int(G), c_int(d), c_int(dv),
-                                                 c_int(v_row), self._stream()), "attention")
+                                                 c_int(v_row), _p(sinks), c_int(1 if zero_sink else 0), _p(slopes),
+                                                 self._stream()), "attention")
 
     def swiglu(self, gu, out, interleaved):
         self._on_gpu(gu, out)
@@ -376,7 +380,7 @@ class NativeBackend:
             self._stream()), "dyt_residual")
 
     def linear_rope_norm_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d, dv,
-                            norm_eps, norm_weights=None, value_mix=None):
+                            norm_eps, norm_weights=None, value_mix=None, pairing="half"):
         self._on_gpu(a, w, bias, cos_sin, positions, slots, q_out, k_cache, v_cache)
         T = a.shape[0]
         part = self._partials(a, w) if self._tc_ok(a, w) else None
@@ -392,15 +396,20 @@ class NativeBackend:
         self._check(self.lib.hfb_rope_norm_kv_write(
             _p(src), c_int(splits), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(cos_sin), c_int(n_rot),
             c_int(cos_sin.shape[0] if cos_sin is not None else 0), _p(positions), _p(slots if G else None), _p(q_out),
-            _p(k_cache if G else None), _p(v_cache if G else None), c_int(_dt(q_out)), c_int64(cache_slots), c_int(T), c_int(H),
+            _p(k_cache if G else None), _p(v_cache if G and dv else None), c_int(_dt(q_out)), c_int64(cache_slots), c_int(T), c_int(H),
             c_int(G), c_int(d), c_int(dv), c_int(0 if norm_eps is None else 1), c_float(norm_eps or 0.0), _p(q_w), _p(k_w),
-            _p(v_first), c_int(v_mode), c_float(v_lambda), self._stream()),
+            _p(v_first), c_int(v_mode), c_float(v_lambda), c_int(1 if pairing == "interleaved" else 0), self._stream()),
             "rope_norm_kv_write")
 
-    def _product_sums(self, a, w, buf):
+    def product_sums(self, a, w, buf, finished=False):
+        self._on_gpu(a, w, buf)
+        src, splits = self._product_sums(a, w, buf, finished)
+        return (src if src.dtype == torch.float32 else src.view(torch.float32)), splits
+
+    def _product_sums(self, a, w, buf, finished=False):
         """float32 sums of a @ w.T for a tail kernel: (partial sums, splits) where the tensor-core product is split over
         k (the tail then sums the pieces itself), else the finished product in ``buf`` with splits = 1."""
-        part = self._partials(a, w) if self._tc_ok(a, w) else None
+        part = self._partials(a, w) if self._tc_ok(a, w) and not finished else None
         if part is not None:
             return part
         self.linear(a, w, None, buf, False)
@@ -473,6 +482,76 @@ class NativeBackend:
             src, splits = part
         self._check(self.lib.hfb_moe_topk(_p(src), c_int(splits), _p(b), c_int(_dt(b) if b is not None else 0), c_int(T), c_int(E),
                                           c_int(top), _p(ids), _p(weights), self._stream()), "moe_topk")
+
+    def moe_route_softmax(self, h, w, correction, top, n_groups, keep, scale, ids, weights, logits):
+        self._on_gpu(h, w, correction, ids, weights, logits)
+        T, E = logits.shape
+        src, splits = self._product_sums(h, w, logits)
+        self._check(self.lib.hfb_moe_route_softmax(_p(src), c_int(splits), _p(correction), c_int(_dt(correction) if correction is not None else 0),
+                                                   c_int(T), c_int(E), c_int(top), c_int(n_groups), c_int(keep), c_float(scale), _p(ids),
+                                                   _p(weights), self._stream()), "moe_route_softmax")
+
+    # ---- hyper-connections ----------------------------------------------------------------------------------
+    def hc_spread(self, emb, x, S):
+        self._on_gpu(emb, x)
+        T, E = emb.shape
+        self._check(self.lib.hfb_hc_spread(_p(emb), _p(x), c_int(S), c_int(T), c_int(E), self._stream()), "hc_spread")
+
+    def hc_in_norm(self, x, S, in_w, rows, norm, out):
+        n = norm or (None, None, None)
+        self._on_gpu(x, in_w, rows, out, *n)
+        M, E = out.shape
+        self._check(self.lib.hfb_hc_in_norm(_p(x), c_int(S), _p(in_w), _p(rows), _p(n[0]), _p(n[1]), _p(n[2]),
+                                            c_int(_dt(n[1]) if norm else 0), _p(out), c_int(_dt(out)), c_int(M), c_int(E),
+                                            self._stream()), "hc_in_norm")
+
+    def hc_update(self, x, S, sources, mix, scale, hc_mix, hc_out, next_in, next_norm, out):
+        n = next_norm or (None, None, None)
+        my, mw, mids, n_real, mh = mix or (None, None, None, 0, None)
+        self._on_gpu(x, my, mw, mids, mh, scale, hc_mix, hc_out, next_in, out, *n)
+        src = list(sources) + [(None, 0, 0.0)] * (2 - len(sources))
+        T, E = x.shape[0], x.shape[1] // S
+        self._check(self.lib.hfb_hc_update(
+            _p(x), c_int(S), _p(src[0][0]), c_int(src[0][1]), c_float(src[0][2]), _p(src[1][0]), c_int(src[1][1]), c_float(src[1][2]),
+            _p(my), _p(mw), _p(mids), c_int(mw.shape[1] if mw is not None else 0), c_int(n_real), _p(mh),
+            c_int(_dt(mh) if mh is not None else 0), _p(scale), c_int(_dt(scale) if scale is not None else 0), _p(hc_mix), _p(hc_out),
+            _p(next_in), _p(n[0]), _p(n[1]), _p(n[2]), c_int(_dt(n[1]) if next_norm else 0), _p(out),
+            c_int(_dt(out) if out is not None else 0), c_int(T), c_int(E), self._stream()), "hc_update")
+
+    # ---- recurrent mixers -----------------------------------------------------------------------------------
+    def decay(self, z, splits, bias, rate, sign, out, H, d, z_stride, z_col0):
+        self._on_gpu(bias, rate, out)
+        self._check(self.lib.hfb_decay(_p(z), c_int(splits), c_int(z_stride), c_int(z_col0), _p(bias),
+                                       c_int(_dt(bias) if bias is not None else 0), _p(rate), c_float(sign), _p(out),
+                                       c_int(out.shape[0]), c_int(H), c_int(d), self._stream()), "decay")
+
+    def short_conv(self, x, splits, w, carried, ctx, out, n_a, d_a, n_b, d_b, n_unit, n_scaled, scale, unit_eps):
+        self._on_gpu(w, out, ctx.token_seq, ctx.cu_tokens, ctx.seq_slots)
+        taps = w.shape[1]
+        self._check(self.lib.hfb_short_conv(
+            _p(x), c_int(splits), _p(w), c_int(_dt(w)), c_int(taps), _p(carried), c_int64(carried.stride(0)), _p(ctx.token_seq),
+            _p(ctx.cu_tokens), _p(ctx.seq_slots), c_int(carried.shape[0]), c_int(ctx.num_seqs), _p(out), c_int(out.shape[0]),
+            c_int(n_a), c_int(d_a), c_int(n_b), c_int(d_b), c_int(n_unit), c_int(n_scaled), c_float(scale), c_float(unit_eps),
+            self._stream()), "short_conv")
+        if taps > 1:
+            self.launches += 1
+
+    def linear_scan(self, q, k, v, a, beta_logit, q_scale, state, ctx, o, H, Hq, d, dv):
+        self._on_gpu(ctx.cu_tokens, ctx.seq_slots)
+        for t in (q, k, v, a, beta_logit, o):
+            if t is not None and not t.is_cuda:
+                raise KernelError("kernel arguments must be CUDA tensors")
+        self._check(self.lib.hfb_linear_scan(
+            _p(q), c_int(q.stride(0)), _p(k), c_int(k.stride(0)), _p(v), c_int(v.stride(0)), _p(a), c_int(a.stride(0)),
+            _p(beta_logit), c_int(beta_logit.stride(0) if beta_logit is not None else 0), c_float(q_scale), _p(state),
+            c_int64(state.stride(0)), _p(ctx.cu_tokens), _p(ctx.seq_slots), c_int(state.shape[0]), c_int(ctx.num_seqs), _p(o),
+            c_int(o.stride(0)), c_int(H), c_int(Hq), c_int(d), c_int(dv), self._stream()), "linear_scan")
+
+    def gate_norm(self, o, w, eps, g, g_splits, g_stride, g_col0, gate, out, H, dv):
+        self._on_gpu(o, w, out)
+        self._check(self.lib.hfb_gate_norm(_p(o), _p(w), c_int(_dt(w)), c_float(eps), _p(g), c_int(g_splits), c_int(g_stride),
+                                           c_int(g_col0), c_int(gate), _p(out), c_int(_dt(out)), c_int(o.shape[0]), c_int(H), c_int(dv),
+                                           self._stream()), "gate_norm")
 
     def moe_group(self, ids, experts, order, tile_expert, tile_p0, tile_n, n_tiles, tile):
         self._on_gpu(ids, order, tile_expert, tile_p0, tile_n, n_tiles)

@@ -111,8 +111,15 @@ class Model:
     # ---- forward ------------------------------------------------------------------------
     def forward(self, ctx) -> Optional[torch.Tensor]:
         T = ctx.token_ids.shape[0]
+        S = self.plan.streams
         x = ctx.buf("residual", (T, self.plan.hidden_size), torch.float32)
         self.embedding.forward(ctx.token_ids, x, ctx=ctx, state=ctx.entry_state(EMBEDDING_STATE))
+        if S > 1:
+            # the stream in S copies, a token's copies side by side, all equal to the embedding at the start
+            emb, x = x, ctx.buf("residual_copies", (T, S * self.plan.hidden_size), torch.float32)
+            from .. import kernels
+            with kernels.phase("glue"):
+                kernels.hc_spread(emb, x, S)
         schedule = self.plan.schedule
         xn = None                                # norm1 of the coming block, when the previous block computed it
         for i, e in enumerate(schedule):
@@ -120,19 +127,34 @@ class Model:
             owner = i if e.cache_of is None else e.cache_of
             # the norm that follows this block: the next block's first, or, after the last block of a step whose
             # tokens all want their logits (a step of single tokens), the final norm
+            extra = layer.post_norms()
             if i + 1 < len(schedule):
                 next_norm = self.layers[schedule[i + 1].layer].norm1
+                if getattr(layer.block, "wants_next_block", False):
+                    extra["next_block"] = self.layers[schedule[i + 1].layer].block
             else:
                 next_norm = self.final_norm if getattr(ctx, "logits_for_all", False) else None
             xn = layer.block.forward(ctx, x, layer.norm1, layer.mixer, layer.norm2, layer.ffn,
                                      ctx.entry_cache(owner), ctx.entry_state(i), e.cache_of is None,
-                                     xn_ready=xn, next_norm=next_norm, **layer.post_norms())
+                                     xn_ready=xn, next_norm=next_norm, **extra)
         M = ctx.num_logit_rows
         if M == 0:
             return None
         if xn is None or not schedule:
             xn = ctx.buf("head_xn", (M, self.plan.hidden_size), self.run_dtype)
-            self.final_norm.forward(x, xn, rows=ctx.logit_rows)
+            if S > 1:
+                # the head reads the sum of the copies
+                from .. import kernels
+                params = getattr(self.final_norm, "params", None)
+                with kernels.phase("glue"):
+                    if params is not None:
+                        kernels.hc_in_norm(x, S, None, ctx.logit_rows, params, xn)
+                    else:
+                        total = ctx.buf("head_sum", (M, self.plan.hidden_size), torch.float32)
+                        kernels.hc_in_norm(x, S, None, ctx.logit_rows, None, total)
+                        self.final_norm.forward(total, xn)
+            else:
+                self.final_norm.forward(x, xn, rows=ctx.logit_rows)
         logits = ctx.buf("logits", (M, self.plan.vocab_size), torch.float32)
         self.head.forward(xn, logits)
         return logits

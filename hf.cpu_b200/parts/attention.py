@@ -19,6 +19,11 @@ sees the earlier keys of its own chunk of that many positions, chunks counted fr
 they are, and it leaves them behind for the step's other layers); "later" replaces a layer's values by
 ``(1 - lambda) v + lambda v_first`` before they are cached, ``lambda`` being the scalar tensor ``v_mix_tensor`` and
 ``v_first`` the same token's values of the "first" layer, whose value heads must have the same count and size.
+``sink``: "learned" adds exp(sink_h) to the softmax's denominator, sink_h a stored number per head (tensor ``sink_tensor``)
+that has no key, no value and no scale; "zero" does the same with a score of 0 (one is added to the denominator).
+``distance_slope_exp`` = c: ``2^(-c (h + 1) / H) * (i - j)`` is taken off the score of query i and key j in head h.
+``values_are_keys``: the layer has no value projection, a key as it is cached also serves as its value (one array of
+rows in the cache).  A rotary encoding with the pairing "interleaved" turns the dimensions (2i, 2i + 1) together.
 """
 from __future__ import annotations
 
@@ -48,6 +53,17 @@ class OutputProduct:
         with kernels.phase("wo"):
             return post.add_product_into(att, self.w_o, self.b_o, y_buf, residual, next_norm, out)
 
+    def forward_sources(self, ctx, xn, cache, state, write_cache, y_buf, finished=False):
+        """The mixer's output as float32 sums for a block that adds it to the stream in a pass of its own: [(planes,
+        splits)] of the output product (``y_buf`` [T, E] float32 holds it where it is not split, and always with
+        ``finished``)."""
+        att = self._attend(ctx, xn, cache, write_cache) if state is None else self._attend(ctx, xn, cache, write_cache, state)
+        with kernels.phase("wo"):
+            if self.b_o is not None:
+                kernels.linear(att, self.w_o, self.b_o, y_buf, accumulate=False)
+                return [(y_buf, 1)]
+            return [kernels.product_sums(att, self.w_o, y_buf, finished)]
+
     def forward_then_norm(self, ctx, xn, residual, cache, state, write_cache, norm, out):
         args = norm.fused_args()
         if args is None:
@@ -67,11 +83,19 @@ class PagedAttention(OutputProduct, Mixer):
                  qkv_bias: bool, out_bias: bool, window: int, position, prefix: str,
                  positions=None, names=None, scale=None, v_head_dim=None, qk_norm_eps=None, own_kv: bool = True,
                  bias_suffix: str = ".bias", weight_suffix: str = ".weight", qk_norm_weights=None, chunk: int = 0,
-                 v_mix=None, v_mix_tensor: str = "vmix", **_):
+                 v_mix=None, v_mix_tensor: str = "vmix", sink=None, sink_tensor: str = "sink", distance_slope_exp=None,
+                 values_are_keys: bool = False, **_):
         self.E, self.H, self.G, self.d = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
         if self.H % self.G:
             raise UnsupportedError(f"unsupported attention geometry: {self.H} heads over {self.G} key/value heads")
         self.dv = int(v_head_dim) if v_head_dim else self.d
+        self.values_are_keys = bool(values_are_keys)
+        if self.values_are_keys and (self.dv != self.d or v_mix or not own_kv):
+            raise UnsupportedError("keys that serve as values have their size, are not mixed, and are the layer's own")
+        if sink not in (None, "zero", "learned"):
+            raise UnsupportedError(f"attention sink '{sink}' is not known (zero, learned)")
+        self.sink = sink
+        self.slope_exp = None if distance_slope_exp is None else float(distance_slope_exp)
         self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
         self.own_kv = bool(own_kv)
         # the q|k|v tail that normalises heads also takes the other two options; the reference's layer keeps its own
@@ -83,7 +107,9 @@ class PagedAttention(OutputProduct, Mixer):
             raise UnsupportedError("a layer without values of its own cannot mix them")
         if qk_norm_weights and self.qk_norm_eps is None:
             raise UnsupportedError("weights on the query and key norm need that norm (qk_norm_eps)")
-        self.general = (self.qk_norm_eps is not None or self.dv != self.d or not self.own_kv or self.v_mix is not None)
+        self.general = (self.qk_norm_eps is not None or self.dv != self.d or not self.own_kv or self.v_mix is not None
+                        or self.values_are_keys or self.sink is not None or self.slope_exp is not None
+                        or getattr((positions or {}).get(position), "pairing", "half") != "half")
         if self.general:
             if not (0 < self.d <= kernels.MAX_HEAD_DIM and 0 < self.dv <= kernels.MAX_HEAD_DIM):
                 raise UnsupportedError(f"head sizes {self.d} / {self.dv} are not supported (1 to {kernels.MAX_HEAD_DIM})")
@@ -95,8 +121,7 @@ class PagedAttention(OutputProduct, Mixer):
         self.rotary = (positions or {}).get(position) if position else None
         if position and self.rotary is None:
             raise UnsupportedError(f"attention names position encoding '{position}', which the plan does not define")
-        if self.rotary is not None and getattr(self.rotary, "pairing", "half") != "half":
-            raise UnsupportedError("this attention rotates pairs (i, i + n_rot/2) only")
+        self.pairing = getattr(self.rotary, "pairing", "half") if self.rotary is not None else "half"
         n = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"}
         n.update(names or {})
         self.names = {k: f"{prefix}.{v}" for k, v in n.items()}
@@ -104,6 +129,8 @@ class PagedAttention(OutputProduct, Mixer):
         if self.norm_names and set(self.norm_names) != {"q", "k"}:
             raise UnsupportedError("qk_norm_weights names one weight for q and one for k")
         self.v_mix_name = f"{prefix}.{v_mix_tensor}" if self.v_mix else None
+        self.sink_name = f"{prefix}.{sink_tensor}" if self.sink == "learned" else None
+        self.sinks = self.slopes = None          # float32 [H]
         self.scale = 1.0 / math.sqrt(self.d) if scale is None else float(scale)
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
         self.norm_w = None              # (q weight, k weight), float32
@@ -119,14 +146,15 @@ class PagedAttention(OutputProduct, Mixer):
 
     @property
     def VD(self):
-        return self.G * self.dv
+        return 0 if self.values_are_keys else self.G * self.dv
 
     @property
     def OD(self):
         return self.H * self.dv
 
     def cache_spec(self):
-        return CacheSpec(self.G, self.d, self.window, 0 if self.dv == self.d else self.dv, chunk=self.chunk)
+        return CacheSpec(self.G, self.d, self.window, 0 if self.dv == self.d else self.dv, chunk=self.chunk,
+                         values_in_keys=self.values_are_keys)
 
     def step_arrays_key(self):
         return ("paged_attention_tiles", self.H // self.G)
@@ -137,7 +165,9 @@ class PagedAttention(OutputProduct, Mixer):
 
     def _projections(self):
         """(key of ``names``, output features) of the projections in the fused product's row order."""
-        return [("q", self.QD)] + ([("k", self.KD), ("v", self.VD)] if self.own_kv else [])
+        if not self.own_kv:
+            return [("q", self.QD)]
+        return [("q", self.QD), ("k", self.KD)] + ([] if self.values_are_keys else [("v", self.VD)])
 
     def tensor_specs(self):
         s = [TensorSpec(self.names[x] + self.wsuf, (n, self.E)) for x, n in self._projections()]
@@ -149,6 +179,8 @@ class PagedAttention(OutputProduct, Mixer):
         s += [TensorSpec(self.norm_names[x], (self.d,), init="norm") for x in sorted(self.norm_names)]
         if self.v_mix_name:
             s.append(TensorSpec(self.v_mix_name, (), init="half"))       # the first layer's is stored too, and unused
+        if self.sink_name:
+            s.append(TensorSpec(self.sink_name, (self.H,)))
         return s
 
     def bind(self, tensors, run_dtype, device):
@@ -164,6 +196,11 @@ class PagedAttention(OutputProduct, Mixer):
         if self.v_mix_name:
             lam = tensors[self.v_mix_name]
             self.v_lambda = float(lam.to(torch.float32).reshape(-1)[0].item()) if self.v_mix == "later" else 0.0
+        if self.sink_name:
+            self.sinks = tensors[self.sink_name].to(torch.float32).contiguous()
+        if self.slope_exp is not None:
+            h = torch.arange(1, self.H + 1, dtype=torch.float64)
+            self.slopes = torch.pow(2.0, -self.slope_exp * h / self.H).to(torch.float32).to(device)
 
     def weight_bytes(self):
         return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.b_qkv, self.w_o, self.b_o)
@@ -192,15 +229,17 @@ class PagedAttention(OutputProduct, Mixer):
         if self.general:
             # the product's sums stay float32 until rotation and the heads' normalisation are done
             G = self.G if self.own_kv else 0
-            qkv = ctx.buf("attn_qkv32", (T, self.QD + G * (self.d + self.dv)), torch.float32)
+            dv_row = 0 if self.values_are_keys else self.dv
+            qkv = ctx.buf("attn_qkv32", (T, self.QD + G * (self.d + dv_row)), torch.float32)
             mix = None
             if self.v_mix:
                 first = ctx.buf(self.V_FIRST, (T, self.VD), torch.float32)
                 mix = (first, 1 if self.v_mix == "first" else 2, self.v_lambda)
             with kernels.phase("qkv"):
                 kernels.linear_rope_norm_kv(xn, self.w_qkv, self.b_qkv, qkv, cos_sin, n_rot, ctx.positions,
-                                            meta.slots if write_cache else None, q, cache.k, cache.v, self.H, G, self.d,
-                                            self.dv, self.qk_norm_eps, norm_weights=self.norm_w, value_mix=mix)
+                                            meta.slots if write_cache else None, q, cache.k, None if self.values_are_keys else cache.v,
+                                            self.H, G, self.d, dv_row, self.qk_norm_eps, norm_weights=self.norm_w, value_mix=mix,
+                                            pairing=self.pairing)
         else:
             qkv = ctx.buf("attn_qkv", (T, self.QD + 2 * self.KD), xn.dtype)
             with kernels.phase("qkv"):
@@ -208,8 +247,10 @@ class PagedAttention(OutputProduct, Mixer):
                                        meta.slots if write_cache else None, q, cache.k, cache.v, self.H, self.G, self.d)
         att = ctx.buf("attn_out", (T, self.OD), xn.dtype)
         with kernels.phase("attn"):
-            kernels.paged_attention(q, cache.k, cache.v, meta, ctx, self.H, self.G, self.d,
-                                    self.mask, self.scale, att, tiles=ctx.arrays(self.step_arrays_key()), dv=self.dv)
+            kernels.paged_attention(q, cache.k, None if self.values_are_keys else cache.v, meta, ctx, self.H, self.G, self.d,
+                                    self.mask, self.scale, att, tiles=ctx.arrays(self.step_arrays_key()), dv=self.dv,
+                                    values_in_keys=self.values_are_keys, sinks=self.sinks, zero_sink=self.sink == "zero",
+                                    slopes=self.slopes)
         return att
 
 

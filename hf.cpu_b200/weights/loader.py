@@ -57,6 +57,7 @@ class WeightError(ValueError):
 class TensorSpec:
     name: str
     shape: Tuple[int, ...]
+    # (an extent of -1: whatever the stored tensor has; such a tensor cannot be made at random)
     init: str = "normal"        # "normal": N(0, std); "norm": 1 + N(0, std/2); "half": 0.5 + N(0, std/2); "int": small integers
     optional: bool = False
 
@@ -319,8 +320,10 @@ def check_against_specs(where: str, specs: Sequence[TensorSpec], have: Dict[str,
     want = {s.name: s for s in specs}
     missing = [s.name for s in specs if s.name not in have and not s.optional]
     unexpected = sorted(set(have) - set(want))
+    def fits(got, declared):         # a declared extent of -1 is one that the stored tensor decides
+        return len(got) == len(declared) and all(w == -1 or g == w for g, w in zip(got, declared))
     misshapen = [(n, have[n][1], tuple(want[n].shape)) for n in sorted(set(have) & set(want))
-                 if tuple(have[n][1]) != tuple(want[n].shape)]
+                 if not fits(tuple(have[n][1]), tuple(want[n].shape))]
     other = [f"tensor '{n}' has dtype {have[n][0]}, which is neither floating nor integer"
              for n in sorted(set(have) & set(want)) if have[n][0] == torch.bool]
     other += [f"tensor '{n}' is not in the file the index names for it" for n in misplaced

@@ -23,6 +23,9 @@ def _seed_for(seed: int, name: str) -> int:
 
 
 def _draw(s: TensorSpec, seed: int, dtype: torch.dtype, device: torch.device, std: float) -> torch.Tensor:
+    if any(n < 0 for n in s.shape):
+        raise ValueError(f"tensor '{s.name}' has an extent that only a stored tensor decides; give it in the configuration "
+                         f"to make the model at random")
     g = torch.Generator(device=device)
     g.manual_seed(_seed_for(seed, s.name))
     if s.init == "int":

@@ -62,7 +62,8 @@ class EmuBackend:
         kf[slots[ok].long()] = rot(x[:, H:H + G])[ok].to(k_cache.dtype)
         vf[slots[ok].long()] = x[:, H + G:][ok].to(v_cache.dtype)
 
-    def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None, dv=None):
+    def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None, dv=None, sinks=None,
+                        zero_sink=False, slopes=None):
         T = q.shape[0]
         bs = meta.block_size
         dv = d if dv is None else dv
@@ -84,7 +85,13 @@ class EmuBackend:
             for h in range(H):
                 g = h // (H // G)
                 s = (k[:, g] @ qf[t, h]) * scale
-                p = torch.softmax(s, 0)
+                if slopes is not None:
+                    s = s - slopes[h] * (pos - torch.arange(lo, pos + 1, device=q.device)).float()
+                if sinks is not None or zero_sink:
+                    sk = sinks[h].reshape(1) if sinks is not None else torch.zeros(1, device=q.device)
+                    p = torch.softmax(torch.cat([s, sk]), 0)[:-1]
+                else:
+                    p = torch.softmax(s, 0)
                 res[t, h] = p @ v[:, g]
         out.copy_(res.view(T, H * dv).to(out.dtype))
 
@@ -133,12 +140,14 @@ class EmuBackend:
         self.dyt_residual(y_buf, post, residual, nxt, out, mix=mix)
 
     def linear_rope_norm_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d, dv,
-                            norm_eps, norm_weights=None, value_mix=None):
+                            norm_eps, norm_weights=None, value_mix=None, pairing="half"):
         self.linear(a, w, bias, qkv_buf, False)
         T = a.shape[0]
 
         def finish(v, weight=None):                    # [T, heads, d]
-            if n_rot:
+            if n_rot and pairing == "interleaved":
+                v = torch.cat([self._rotate_pairs(v[..., :n_rot], cos_sin, positions), v[..., n_rot:]], -1)
+            elif n_rot:
                 half = n_rot // 2
                 cs = cos_sin[positions.long()]
                 c, s = cs[:, None, :, 0], cs[:, None, :, 1]
@@ -163,7 +172,8 @@ class EmuBackend:
             else:
                 v = (1.0 - lam) * v + lam * first.view(T, G, dv)
         k_cache.view(-1, G, d)[slots[ok].long()] = k[ok].to(k_cache.dtype)
-        v_cache.view(-1, G, dv)[slots[ok].long()] = v[ok].to(v_cache.dtype)
+        if dv:
+            v_cache.view(-1, G, dv)[slots[ok].long()] = v[ok].to(v_cache.dtype)
 
     @staticmethod
     def _rotate_pairs(v, cos_sin, positions):
@@ -233,12 +243,123 @@ class EmuBackend:
         ids.copy_(idx[:, :top].int())
         weights.copy_(torch.softmax(zc[:, :top], -1))
 
+    def moe_route_softmax(self, h, w, correction, top, n_groups, keep, scale, ids, weights, logits):
+        z = h.float() @ w.float().T
+        logits.copy_(z)
+        s = torch.softmax(z, -1)
+        ch = s + correction.float() if correction is not None else s.clone()
+        T, E = s.shape
+        if n_groups > 1 and keep < n_groups:
+            per = E // n_groups
+            best = ch.view(T, n_groups, per).max(-1).values
+            kept = torch.sort(best, dim=-1, descending=True, stable=True).indices[:, :keep]
+            allow = torch.zeros(T, n_groups, dtype=torch.bool, device=s.device)
+            allow.scatter_(1, kept, True)
+            ch = torch.where(allow[:, :, None].expand(T, n_groups, per).reshape(T, E), ch, torch.full_like(ch, float("-inf")))
+        idx = torch.sort(ch, dim=-1, descending=True, stable=True).indices[:, :top]
+        ids.copy_(idx.int())
+        weights.copy_(torch.gather(s, 1, idx) * scale)
+
+    def product_sums(self, a, w, buf, finished=False):
+        self.linear(a, w, None, buf, False)
+        return buf, 1
+
+    # ---- hyper-connections ----
+    def hc_spread(self, emb, x, S):
+        x.copy_(emb.repeat(1, S))
+
+    def hc_in_norm(self, x, S, in_w, rows, norm, out):
+        xr = (x if rows is None else x[rows.long()]).view(-1, S, out.shape[1])
+        u = xr.sum(1) if in_w is None else (in_w[None, :, None] * xr).sum(1)
+        out.copy_((self._dyt(u, norm) if norm is not None else u).to(out.dtype))
+
+    def hc_update(self, x, S, sources, mix, scale, hc_mix, hc_out, next_in, next_norm, out):
+        T = x.shape[0]
+        E = x.shape[1] // S
+        y = torch.zeros(T, E, dtype=torch.float32, device=x.device)
+        for src, splits, factor in sources:
+            y = y + factor * src.reshape(-1)[:splits * T * E].view(splits, T, E).sum(0)
+        if mix is not None:
+            my, mw, mids, n_real, mh = mix
+            rows = my.view(T, mw.shape[1], E)
+            if mids is not None:
+                rows = torch.where((mids >= n_real)[:, :, None], mh.float()[:, None, :], rows)
+            y = y + (mw[:, :, None] * rows).sum(1)
+        if scale is not None:
+            y = y * scale.float()
+        old = x.view(T, S, E).clone()
+        new = torch.einsum("sd,tse->tde", hc_mix, old) + hc_out[None, :, None] * y[:, None, :]
+        x.copy_(new.reshape(T, S * E))
+        if out is not None:
+            u = new.sum(1) if next_in is None else (next_in[None, :, None] * new).sum(1)
+            out.copy_((self._dyt(u, next_norm) if next_norm is not None else u).to(out.dtype))
+
+    # ---- recurrent mixers ----
+    def decay(self, z, splits, bias, rate, sign, out, H, d, z_stride, z_col0):
+        T = out.shape[0]
+        v = z.reshape(-1)[:splits * T * z_stride].view(splits, T, z_stride).sum(0)[:, z_col0:z_col0 + H * d]
+        if bias is not None:
+            v = v + bias.float()
+        sp = torch.nn.functional.softplus(sign * v, threshold=20.0)
+        out.copy_(torch.exp(-rate.repeat_interleave(d)[None, :] * sp))
+
+    def short_conv(self, x, splits, w, carried, ctx, out, n_a, d_a, n_b, d_b, n_unit, n_scaled, scale, unit_eps):
+        T, C = out.shape
+        xs = x.reshape(-1)[:splits * T * C].view(splits, T, C).sum(0)
+        taps = w.shape[1]
+        K = taps - 1
+        wf = w.float()
+        cu, slots = ctx.cu_tokens.tolist(), ctx.seq_slots.tolist()
+        for s in range(len(slots)):
+            a, b = cu[s], cu[s + 1]
+            hist = torch.cat([carried[slots[s]][:K], xs[a:b]]) if K else xs[a:b]
+            y = sum(hist[i:i + (b - a)] * wf[:, i] for i in range(taps))
+            out[a:b] = y * torch.sigmoid(y)
+            if K:
+                carried[slots[s]][:K] = hist[hist.shape[0] - K:]
+        at = 0
+        for u in range(n_a + n_b):
+            n = d_a if u < n_a else d_b
+            if u < n_unit:
+                seg = out[:, at:at + n]
+                r = 1.0 / torch.sqrt((seg * seg).sum(-1, keepdim=True) + unit_eps)
+                out[:, at:at + n] = seg * r * (scale if u < n_scaled else 1.0)
+            at += n
+
+    def linear_scan(self, q, k, v, a, beta_logit, q_scale, state, ctx, o, H, Hq, d, dv):
+        cu, slots = ctx.cu_tokens.tolist(), ctx.seq_slots.tolist()
+        rep = H // Hq
+        for s in range(len(slots)):
+            S = state[slots[s]].transpose(1, 2).clone()              # [H, d, dv]
+            for t in range(cu[s], cu[s + 1]):
+                qt = q[t].view(Hq, d).repeat_interleave(rep, 0)
+                kt = k[t].view(Hq, d).repeat_interleave(rep, 0)
+                vt, at = v[t].view(H, dv), a[t].view(H, d)
+                S = at[:, :, None] * S
+                u = vt
+                if beta_logit is not None:
+                    u = torch.sigmoid(beta_logit[t])[:, None] * (vt - torch.einsum("hij,hi->hj", S, kt))
+                S = S + kt[:, :, None] * u[:, None, :]
+                o[t] = (torch.einsum("hij,hi->hj", S, qt) * q_scale).reshape(-1)
+            state[slots[s]] = S.transpose(1, 2)
+
+    def gate_norm(self, o, w, eps, g, g_splits, g_stride, g_col0, gate, out, H, dv):
+        T = o.shape[0]
+        gz = g.reshape(-1)[:g_splits * T * g_stride].view(g_splits, T, g_stride).sum(0)[:, g_col0:g_col0 + H * dv].reshape(T, H, dv)
+        x = o.view(T, H, dv)
+        y = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w.float()
+        y = y * (gz * torch.sigmoid(gz) if gate == 0 else torch.sigmoid(gz))
+        out.copy_(y.reshape(T, H * dv).to(out.dtype))
+
     def moe_group(self, ids, experts, order, tile_expert, tile_p0, tile_n, n_tiles, tile):
         MOE_TILE = tile
         flat = ids.reshape(-1)
         srt = torch.sort(flat, stable=True).indices.int()
         order[:flat.numel()] = srt
-        counts = torch.bincount(flat.long(), minlength=experts).tolist()
+        keep = flat < experts                    # an id beyond the experts takes no place
+        srt = srt[keep[srt.long()]]
+        order[:srt.numel()] = srt
+        counts = torch.bincount(flat[keep].long(), minlength=experts).tolist()
         n = at = 0
         for e, c in enumerate(counts):
             for p0 in range(0, c, MOE_TILE):
@@ -255,7 +376,11 @@ class EmuBackend:
             pairs = order[places].long()
             src = pairs // src_div if src_div else places
             dst = pairs if scatter else places
-            out[dst] = self._activate(a[src].float() @ w[e].float().T, act).to(out.dtype)
+            z = a[src].float() @ w[e].float().T
+            if act >> 8:
+                out[dst] = (self._activate(z[:, 0::2], act & 255) * z[:, 1::2]).to(out.dtype)
+            else:
+                out[dst] = self._activate(z, act).to(out.dtype)
 
     def moe_combine(self, y, weights, out):
         T, top = weights.shape

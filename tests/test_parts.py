@@ -76,10 +76,11 @@ def test_rotary_part_table():
     inter = make_part("position", PartSpec("rotary", {"head_dim": 48, "n_rot": 32, "theta": 12345.0, "pairing": "interleaved"}))
     inter.prepare(300, torch.device("cpu"))
     assert torch.equal(inter.cos_sin, rot.cos_sin)
-    with pytest.raises(UnsupportedError):
-        make_part("mixer", PartSpec("paged_attention", {"hidden_size": 64, "num_heads": 2, "num_kv_heads": 2, "head_dim": 48,
-                                                        "qkv_bias": False, "out_bias": False, "window": 0, "position": "r",
-                                                        "prefix": "a"}), positions={"r": inter})
+    # the attention part takes both pairings; the interleaved one goes through the tail kernel that knows it
+    att = make_part("mixer", PartSpec("paged_attention", {"hidden_size": 64, "num_heads": 2, "num_kv_heads": 2, "head_dim": 48,
+                                                          "qkv_bias": False, "out_bias": False, "window": 0, "position": "r",
+                                                          "prefix": "a"}), positions={"r": inter})
+    assert att.pairing == "interleaved" and att.general
     with pytest.raises(UnsupportedError):
         make_part("position", PartSpec("rotary", {"head_dim": 48, "n_rot": 32, "theta": 1.0, "pairing": "quarter"}))
     with pytest.raises(UnsupportedError):
