@@ -279,7 +279,43 @@ def peludra_configs(z):
     return peludra, qwen
 
 
-COMPARISONS = {"manapel": (COMPARE_SIZES, compare_configs), "peludra": (PELUDRA_SIZES, peludra_configs)}
+# ---- `--compare mokisun`: the Mokisun design beside the Manapel design at equal layer sizes --------------------------
+# Layers in threes: gated linear attention, windowed attention with sinks, and attention on its own keys beside a gated
+# delta rule; every layer with a routed feed-forward.  The Manapel twin has attention with as many heads of the same
+# size in every layer and routed experts with as many weights per token (its experts are not gated: 2 F' = 3 F).
+MOKISUN_SIZES = {
+    "w1024_h64": dict(width=1024, heads=16, kv=4, dim=64, rot=32, window=512, rheads=8, rdim=64, rv=128, rank=64, experts=14, identity=2,
+                      top=2, ff=512, groups=(4, 2), layers=6, vocab=32768),
+    "w2048_h128": dict(width=2048, heads=16, kv=4, dim=128, rot=64, window=1024, rheads=16, rdim=128, rv=128, rank=128, experts=28,
+                       identity=4, top=4, ff=1024, groups=(8, 4), layers=6, vocab=32768),
+    "w4096_h128": dict(width=4096, heads=32, kv=8, dim=128, rot=128, window=1024, rheads=32, rdim=128, rv=128, rank=256, experts=28,
+                       identity=4, top=4, ff=2048, groups=(8, 4), layers=3, vocab=32768),
+}
+
+
+def mokisun_configs(z):
+    att = dict(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, mask=dict(size=z["window"]))
+    gla = dict(type="gla", mixer=dict(heads=z["rheads"], dim=z["rdim"], vdim=z["rv"], tau=16.0, a_rank=z["rank"]))
+    attention = dict(type="attention", mixer=dict(att, rot=dict(dims=z["rot"], base=10000.0)))
+    parallel = dict(type="parallel", mixer=dict(
+        left=att, left_scale=1.0, right_scale=1.0,
+        right=dict(heads=z["rheads"], kv_heads=z["rheads"] // 2, dim=z["rdim"], vdim=z["rv"], conv=4, a_rank=z["rank"], g_rank=z["rank"])))
+    mlp = dict(kind="moe", expert=dict(ff=z["ff"]), router=dict(experts=z["experts"], identity=z["identity"], top=z["top"], scale=1.0,
+                                                                 groups=dict(count=z["groups"][0], keep=z["groups"][1])))
+    layers = [dict((gla, attention, parallel)[i % 3], mlp=mlp) for i in range(z["layers"])]
+    mokisun = dict(architecture="Mokisun", vocab=z["vocab"], width=z["width"], streams=2, norm=dict(eps=1e-6), layers=layers,
+                   max_positions=8192)
+    m_att = dict(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, rot=dict(dims=z["rot"], base=10000.0))
+    m_moe = dict(kind="moe", router=dict(experts=z["experts"] + z["identity"], top=z["top"]), expert=dict(ff=3 * z["ff"] // 2))
+    manapel = dict(architecture="Manapel", vocab=z["vocab"], width=z["width"], logit_scale=1.0, norm=dict(eps=1e-5), max_positions=8192,
+                   layers=[dict(type="attention", mixer=m_att, mlp=m_moe) for _ in range(z["layers"])])
+    return mokisun, manapel
+
+
+COMPARISONS = {"manapel": (COMPARE_SIZES, compare_configs), "peludra": (PELUDRA_SIZES, peludra_configs),
+               "mokisun": (MOKISUN_SIZES, mokisun_configs)}
+# the design each comparison stands beside
+TWINS = {"manapel": "qwen2", "peludra": "qwen2", "mokisun": "manapel"}
 
 
 def phase_work(model, q_len, ctx_len, batch):
@@ -294,9 +330,7 @@ def phase_work(model, q_len, ctx_len, batch):
     def add(k, ops, nbytes):
         work[k][0] += ops
         work[k][1] += nbytes
-    for e in model.plan.schedule:
-        L = model.layers[e.layer]
-        m, f = L.mixer, L.ffn
+    def attention(m):
         dv = getattr(m, "dv", m.d)
         # what the layer's mask lets a query see: (query, key) pairs, and the keys a request's queries read between them
         spec = m.cache_spec()
@@ -312,8 +346,36 @@ def phase_work(model, q_len, ctx_len, batch):
             add("attn", 2.0 * m.H * (m.row + m.R) * pairs + 2.0 * T * m.w_uv.numel(),
                 el * (keys * m.row + T * m.H * (m.row + m.R + m.dv) + m.w_uv.numel()))
         else:
+            kv_row = m.d if getattr(m, "values_are_keys", False) else m.d + dv
             add("qkv", 2.0 * T * m.w_qkv.numel(), el * (m.w_qkv.numel() + T * (m.E + m.w_qkv.shape[0])))
-            add("attn", 2.0 * m.H * (m.d + dv) * pairs, el * (keys * m.G * (m.d + dv) + 2 * T * m.H * m.d))
+            add("attn", 2.0 * m.H * (m.d + dv) * pairs, el * (keys * m.G * kv_row + T * m.H * (m.d + dv)))
+
+    def recurrent(m):
+        # products in front (float32 sums out), then the walk along the tokens: float32 operands in, the state of every
+        # request read and written once, float32 rows out; its operations run on the ordinary float32 units
+        front = [w for w in (m.w_in, m.w_a1, m.w_a2, getattr(m, "w_beta", None), getattr(m, "w_g1", None), getattr(m, "w_g2", None))
+                 if w is not None]
+        n_front = sum(w.numel() for w in front)
+        rows_out = sum(w.shape[0] for w in front)
+        add("qkv", 2.0 * T * n_front, el * (n_front + T * m.E) + 4 * T * rows_out)
+        G = getattr(m, "G", m.H)
+        delta = hasattr(m, "w_beta")
+        add("attn", (8.0 if delta else 6.0) * T * m.H * m.d * m.dv,
+            4 * (T * (2 * G * m.d + m.H * m.d + 2 * m.H * m.dv) + 2 * batch * m.H * m.d * m.dv) + (4 + el) * T * m.H * m.dv)
+        add("wo", 2.0 * T * m.w_o.numel(), el * (m.w_o.numel() + T * m.H * m.dv) + 4 * T * m.E)
+
+    def mixer(m):
+        if hasattr(m, "branches"):
+            for b in m.branches:
+                mixer(b)
+        elif hasattr(m, "w_in"):
+            recurrent(m)
+        else:
+            attention(m)
+    for e in model.plan.schedule:
+        L = model.layers[e.layer]
+        f = L.ffn
+        mixer(L.mixer)
         if hasattr(f, "w_up"):
             add("gate_up", 2.0 * T * f.w_up.numel(), el * (f.w_up.numel() + T * (f.E + f.F)))
             add("down", 2.0 * T * f.w_down.numel(), el * (f.w_down.numel() + T * f.F) + 4 * T * f.E)
@@ -321,14 +383,19 @@ def phase_work(model, q_len, ctx_len, batch):
             add("gate_up", 2.0 * T * f.w_gate_up.numel(), el * (f.w_gate_up.numel() + T * (f.E + f.F)))
             add("down", 2.0 * T * f.w_down.numel(), el * (f.w_down.numel() + T * f.F) + 4 * T * f.E)
         elif f is not None:
-            used = f.n * (1.0 - (1.0 - 1.0 / f.n) ** (T * f.top))
-            add("gate_up", 2.0 * T * f.E * (f.top * f.F + f.FS), el * (f.E * (used * f.F + f.FS) + T * (f.E + f.top * f.F + f.FS)))
-            add("down", 2.0 * T * f.E * (f.top * f.F + f.FS), el * (f.E * (used * f.F + f.FS) + T * (f.top * f.F + f.FS)) + 4 * T * f.E * (f.top + 1))
+            # of n_out router outputs the last are identity experts without weights: a token's `top` choices fall on real
+            # experts in proportion; a gated expert has two matrices in front
+            n_out = getattr(f, "n_out", f.n)
+            top = f.top * f.n / n_out
+            up = 2 if getattr(f, "gated", False) else 1
+            used = f.n * (1.0 - (1.0 - 1.0 / n_out) ** (T * f.top))
+            add("gate_up", 2.0 * T * f.E * up * (top * f.F + f.FS), el * (f.E * up * (used * f.F + f.FS) + T * (f.E + top * f.F + f.FS)))
+            add("down", 2.0 * T * f.E * (top * f.F + f.FS), el * (f.E * (used * f.F + f.FS) + T * (top * f.F + f.FS)) + 4 * T * f.E * (top + 1))
     return work
 
 
 def run_compare(args):
-    """Prefill (one prompt) and decode (a batch of single tokens) of the chosen design and its Qwen2 twin at each size:
+    """Prefill (one prompt) and decode (a batch of single tokens) of the chosen design and the design it stands beside at each size:
     tokens a second, and per phase of the forward pass the device time (CUDA events around the phase's kernels, steps run
     kernel by kernel) with its share of the measured peak, the better of the operations and the bytes the phase needs."""
     import torch
@@ -342,7 +409,7 @@ def run_compare(args):
     P, B = args.prompt, args.batch
     flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda:0")
     for name in names:
-        for arch, cfg_d in zip((args.compare, "qwen2"), configs_of(sizes[name])):
+        for arch, cfg_d in zip((args.compare, TWINS[args.compare]), configs_of(sizes[name])):
             cfg = config_from_dict(cfg_d)
             model = hfcpu_b200.random_model(cfg, seed=1, dtype=torch.bfloat16, device="cuda:0", std=0.02)
             eng = hfcpu_b200.Engine(model, block_size=BLOCK, max_tokens=(B + 1) * (P + 64), max_requests=B + 1, ctx_max=P + 64)
@@ -509,7 +576,8 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), help="run one of the other sized workloads end to end through "
                     "Session.generate instead of the record (c3: 0.5B sizes, mixed chunked prompts and decodes; c4: 32B sizes)")
     ap.add_argument("--compare", choices=sorted(COMPARISONS), help="instead of the record: prefill and decode of that design beside the "
-                    "Qwen2 decoder at equal layer sizes (random weights), one JSON line per size and architecture")
+                    "design closest to it (the Qwen2 decoder; for mokisun, Manapel) at equal layer sizes (random weights), one JSON line per size "
+                    "and architecture")
     ap.add_argument("--sizes", default="", help="with --compare: the sizes to run, with commas (default: all)")
     ap.add_argument("--ref-layers", type=int, default=28, help="layers the reference arm runs (it is a CPU program)")
     ap.add_argument("--ref-timeout", type=int, default=1500, help="seconds the reference arm may take")

@@ -84,15 +84,16 @@ def rotate_interleaved(x, positions, rot):
     return out
 
 
-def windowed_attention(q, k, v, scale, window, sink, slopes=None):
+def windowed_attention(q, k, v, scale, window, sink, slopes=None, rows=None):
     """q [T, H, d], k [T, G, d], v [T, G, dv].  Token i sees j with 0 <= i - j < window.  ``sink`` [H]: a score per head
-    that joins the softmax's denominator and has no value.  ``slopes`` [H]: slope * (i - j) is taken off the score."""
+    that joins the softmax's denominator and has no value.  ``slopes`` [H]: slope * (i - j) is taken off the score.
+    ``rows``: the queries to compute (the others' rows stay zero)."""
     T, H, _ = q.shape
     G = k.shape[1]
     out = np.zeros((T, H, v.shape[2]))
     for h in range(H):
         g = h // (H // G)
-        for i in range(T):
+        for i in (range(T) if rows is None else rows):
             lo = max(0, i - window + 1)
             s = (k[lo:i + 1, g] @ q[i, h]) * scale
             if slopes is not None:
@@ -263,3 +264,13 @@ def forward(cfg, W, tokens, return_layers=False):
         after.append(X.sum(0))
     logits = dynamic_tanh(X.sum(0), W, "final.norm") @ W["head"].T
     return (logits, np.stack(after)) if return_layers else logits
+
+
+def greedy(cfg, W, prompt, n):
+    """n tokens by arg-max, the whole sequence computed anew for each."""
+    ids, out = list(prompt), []
+    for _ in range(n):
+        t = int(np.argmax(forward(cfg, W, ids)[-1]))
+        out.append(t)
+        ids.append(t)
+    return out
