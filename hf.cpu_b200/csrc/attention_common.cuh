@@ -55,6 +55,11 @@ struct AttnParams {
     int max_blocks, block_size, window, H, G, splits;
     long long num_pages;
     float scale_log2;                   // scale * log2(e)
+    // options of the softmax (the decode kernel; null / 0: none): a sink per head [H] or a sink of score zero, a score
+    // without key or value that joins the denominator once; slopes [H]: slope * (query position - key position) is
+    // taken off every score
+    const float *sinks, *slopes;
+    int zero_sink;
 };
 
 // Byte offset of 16-byte chunk `c` of row `row` in a tile whose rows hold D bf16 (D = 64 or 128).

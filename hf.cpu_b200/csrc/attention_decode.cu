@@ -147,6 +147,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const bool v0 = tl0 < nt, v1 = tl1 < nt;
         const int pos0 = v0 ? p.positions[t0 + tl0] : -1, pos1 = v1 ? p.positions[t0 + tl1] : -1;
         const int lo0 = mask_lo(pos0, p.window), lo1 = mask_lo(pos1, p.window);
+        // the distance bias in the exponent's base 2; rows beyond the tile's tokens have none
+        const float sl0 = (p.slopes && v0) ? p.slopes[g * r + row0 % r] * 1.4426950408889634f : 0.f;
+        const float sl1 = (p.slopes && v1) ? p.slopes[g * r + row1 % r] * 1.4426950408889634f : 0.f;
         const int kbase = warp * 16, mi = lane >> 3;
         // the 8 keys whose rows this lane names to ldmatrix lie in one page (pages hold 8 keys or more)
         const int bs = p.block_size;
@@ -175,8 +178,12 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
                 for (int e = 0; e < 2; e++) {
                     float a = sc[i][e] * p.scale_log2, b = sc[i][2 + e] * p.scale_log2;
+                    const int key = kt * ABN + kbase + i * 8 + (lane & 3) * 2 + e;
+                    if (p.slopes) {
+                        a = fmaf(sl0, (float)(key - pos0), a);
+                        b = fmaf(sl1, (float)(key - pos1), b);
+                    }
                     if (edge) {
-                        const int key = kt * ABN + kbase + i * 8 + (lane & 3) * 2 + e;
                         a = (v0 && key >= lo0 && key <= pos0) ? a : -INFINITY;
                         b = (v1 && key >= lo1 && key <= pos1) ? b : -INFINITY;
                     }
@@ -262,6 +269,16 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         }
         const int tok = t0 + row / r, head = g * r + row % r;
         const size_t th = (size_t)tok * p.H + head;
+        if ((p.sinks || p.zero_sink) && split == 0) {
+            // the sink joins the first split's sum as one more score (without a value); the merges of the splits then
+            // carry it like any other
+            const float sk = p.sinks ? p.sinks[head] * 1.4426950408889634f : 0.f;
+            const float top = fmaxf(m, sk);
+            const float f = m == -INFINITY ? 0.f : exp2f(m - top);
+            denom = denom * f + exp2f(sk - top);
+            acc.x *= f; acc.y *= f; acc.z *= f; acc.w *= f;
+            m = top;
+        }
         if (p.splits > 1) {
             *(float4 *)(p.part_o + (th * p.splits + split) * D + 4 * c4) = acc;
             if (c4 == 0) *(float2 *)(p.part_ml + (th * p.splits + split) * 2) = make_float2(m, denom);
@@ -426,11 +443,11 @@ using namespace hfb;
 // CTAs and needs hfb_attention_fast_scratch(T, H, d, splits) bytes of float32 scratch.  The splits are merged in
 // split order: by the CTA that stores a tile's last split, when `counters` (n_tiles * G ints, zero before the first
 // launch; every launch leaves them zero) is given, else by a second kernel.
-extern "C" int hfb_attention_decode(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
+extern "C" int hfb_attention_decode_opt(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
                                     int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
                                     const int32_t *tile_nt, int n_tiles, int stages, int splits, int block_size,
                                     int64_t num_pages, int window, float scale, void *out, void *scratch, size_t scratch_bytes,
-                                    int T, int H, int G, int d, int *counters, int counters_len, hfb_stream s)
+                                    int T, int H, int G, int d, int *counters, int counters_len, const float *sinks, int zero_sink, const float *slopes, hfb_stream s)
 {
     if (n_tiles <= 0) return HFB_OK;
     if (d != 64 && d != 128) return fail(HFB_ENOTSUP, "attention_decode: head_dim %d (64 and 128 only)", d);
@@ -455,6 +472,7 @@ extern "C" int hfb_attention_decode(const void *q, const void *k_cache, const vo
     p.part_o = (float *)scratch; p.part_ml = splits > 1 ? (float *)scratch + (size_t)T * H * splits * d : nullptr;
     p.max_blocks = max_blocks; p.block_size = block_size; p.window = window; p.H = H; p.G = G; p.splits = splits;
     p.num_pages = num_pages; p.scale_log2 = scale * 1.4426950408889634f;
+    p.sinks = sinks; p.slopes = slopes; p.zero_sink = zero_sink;
     p.counters = (splits > 1 && splits <= 64 && counters && counters_len >= n_tiles * G) ? counters : nullptr;
     cudaStream_t st = (cudaStream_t)s;
     if (one_map) rc = d == 128 ? launch_decode_stages<128, true>(stages, mk, mv, p, slots, n_tiles, st)
@@ -463,4 +481,15 @@ extern "C" int hfb_attention_decode(const void *q, const void *k_cache, const vo
                        : launch_decode_stages<64, false>(stages, mk, mv, p, slots, n_tiles, st);
     if (rc != HFB_OK || splits == 1 || p.counters) return rc;
     return launch_attention_combine(p, T, d, st);
+}
+
+extern "C" int hfb_attention_decode(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
+                                    int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
+                                    const int32_t *tile_nt, int n_tiles, int stages, int splits, int block_size,
+                                    int64_t num_pages, int window, float scale, void *out, void *scratch, size_t scratch_bytes,
+                                    int T, int H, int G, int d, int *counters, int counters_len, hfb_stream s)
+{
+    return hfb_attention_decode_opt(q, k_cache, v_cache, block_table, max_blocks, positions, tile_seq, tile_t0, tile_nt, n_tiles,
+                                    stages, splits, block_size, num_pages, window, scale, out, scratch, scratch_bytes, T, H, G, d,
+                                    counters, counters_len, nullptr, 0, nullptr, s);
 }

@@ -301,6 +301,7 @@ extern "C" int hfb_attention_fast(const void *q, const void *k_cache, const void
     if (splits > 1 && (!scratch || scratch_bytes < hfb_attention_fast_scratch(T, H, d, splits)))
         return fail(HFB_EINVAL, "attention_fast: scratch of %zu bytes is too small for %d splits", scratch_bytes, splits);
     AttnParams p;
+    p.sinks = p.slopes = nullptr; p.zero_sink = 0;
     p.q = (const __nv_bfloat16 *)q; p.k_cache = (const __nv_bfloat16 *)k_cache; p.v_cache = (const __nv_bfloat16 *)v_cache;
     p.out = (__nv_bfloat16 *)out; p.block_table = block_table; p.positions = positions;
     p.tile_seq = tile_seq; p.tile_t0 = tile_t0; p.tile_nt = tile_nt;

@@ -44,6 +44,10 @@ struct AttnTc2Params {
     int n_tiles;                                     // double tiles in all
     int num_slots;                                   // pages * block_size: a row coordinate beyond it reads zeros
     float scale_log2;
+    // options of the softmax (null / 0: none): a sink per head [H] or a sink of score zero, a score without key or value
+    // that joins the denominator once; slopes [H]: slope * (query position - key position) is taken off every score
+    const float *sinks, *slopes;
+    int zero_sink;
 };
 
 __device__ __forceinline__ float u_ex2(float x)
@@ -280,6 +284,8 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
             }
             const int pos = valid ? p.positions[t_first + tl] : -1;
             const int lo = mask_lo(pos, p.window);
+            // the distance bias in the exponent's base 2 (rows beyond the tile's tokens have none)
+            const float slope2 = (p.slopes && valid) ? p.slopes[it.g * r + hl] * 1.4426950408889634f : 0.f;
             float m_ref = -INFINITY, l = 0.f;        // the maximum the exponentials refer to, and the sum in its scale
             for (int j = 0; j < n_mine && ok; j++) {
                 const uint32_t ph = (g_mine + j) & 1;
@@ -296,6 +302,15 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                 // (the maximum and the sum each run in four independent chains: with two warps per scheduler a chain of
                 // 128 dependent operations is not hidden by the other warp)
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                float sc = p.scale_log2;
+                if (p.slopes) {
+                    // with a bias the scores are scaled and biased in place first, and the factor below is one
+                    const float b0 = slope2 * (float)(key0 - pos);
+#pragma unroll
+                    for (int c = 0; c < 128; c++)
+                        sv[c] = __float_as_uint(fmaf(__uint_as_float(sv[c]), p.scale_log2, fmaf(slope2, (float)c, b0)));
+                    sc = 1.f;
+                }
                 // rows beyond the tile's tokens (their queries are zeros, nothing of them is written) go with the
                 // rows that see every key, so that their warp is not split over both branches
                 const bool all_visible = !valid || (key0 + U_KEYS - 1 <= pos && key0 >= lo);
@@ -312,7 +327,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                     }
                 }
                 float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-                mx *= p.scale_log2;                                  // scale > 0 commutes with the maximum
+                mx *= sc;                                            // scale > 0 commutes with the maximum
                 // raise the reference only when the row's maximum has outgrown it by 2^TAU (or there was none yet)
                 float corr = 1.f;
                 if (mx > m_ref + U_TAU || (m_ref == -INFINITY && mx > -INFINITY)) {
@@ -324,7 +339,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                 uint32_t pk[64];
 #pragma unroll
                 for (int c = 0; c < 128; c += 2) {
-                    const float a = u_ex2(__uint_as_float(sv[c]) * p.scale_log2 - bs), b = u_ex2(__uint_as_float(sv[c + 1]) * p.scale_log2 - bs);
+                    const float a = u_ex2(__uint_as_float(sv[c]) * sc - bs), b = u_ex2(__uint_as_float(sv[c + 1]) * sc - bs);
                     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
                     const uint32_t hb = *(uint32_t *)&h;            // the sum runs over the rounded values the product uses:
                     sum4[(c >> 1) & 3] += __uint_as_float(hb << 16) + __uint_as_float(hb & 0xffff0000u);   // widened by bit moves, not conversions
@@ -362,6 +377,11 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
             if (ok) ok = mbar_wait(pv_done + 8 * i, (g_mine - 1) & 1, abort_flag, err);
             if (ok) {
                 tc_fence_after();
+                if (p.sinks || p.zero_sink) {
+                    // the sink: one more term of the sum, in the scale of the row's reference maximum
+                    const float sk = p.sinks ? p.sinks[it.g * r + hl] * 1.4426950408889634f : 0.f;
+                    l += exp2f(sk - (m_ref == -INFINITY ? 0.f : m_ref));
+                }
                 const float inv = l > 0.f ? 1.0f / l : 0.f;
                 uint4 *dst = (uint4 *)(p.out + th);
 #pragma unroll 1
@@ -422,10 +442,11 @@ using namespace hfb;
 // Attention of long prompt portions with two query tiles per CTA: bfloat16, head_dim 64 or 128, block sizes 8..128 that
 // divide 128, at most 128 query heads per key/value head.  Tiles (tile_seq, tile_t0, tile_nt) hold at most
 // 2 * (128 / (H/G)) consecutive tokens of one request each.
-extern "C" int hfb_attention_tc2(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
+extern "C" int hfb_attention_tc2_opt(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
                                  int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
                                  const int32_t *tile_nt, int n_tiles, int block_size, int64_t num_pages, int window,
-                                 float scale, void *out, int T, int H, int G, int d, hfb_stream s)
+                                 float scale, void *out, int T, int H, int G, int d, const float *sinks, int zero_sink, const float *slopes,
+                                     hfb_stream s)
 {
     if (n_tiles <= 0) return HFB_OK;
     if (d != 64 && d != 128) return fail(HFB_ENOTSUP, "attention_tc2: head_dim %d (64 and 128 only)", d);
@@ -448,10 +469,20 @@ extern "C" int hfb_attention_tc2(const void *q, const void *k_cache, const void 
     p.per = U_ROWS / (H / G);
     p.n_tiles = n_tiles;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.sinks = sinks; p.slopes = slopes; p.zero_sink = zero_sink;
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long long items = (long long)n_tiles * G;
     const int grid = (int)(items < sms ? items : (sms > 0 ? sms : 1));      // one CTA per SM walks its share of the items
     return d == 128 ? launch_tc2<128>(mk, mv, p, grid, (cudaStream_t)s) : launch_tc2<64>(mk, mv, p, grid, (cudaStream_t)s);
+}
+
+extern "C" int hfb_attention_tc2(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
+                                 int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
+                                 const int32_t *tile_nt, int n_tiles, int block_size, int64_t num_pages, int window,
+                                 float scale, void *out, int T, int H, int G, int d, hfb_stream s)
+{
+    return hfb_attention_tc2_opt(q, k_cache, v_cache, block_table, max_blocks, positions, tile_seq, tile_t0, tile_nt, n_tiles,
+                                 block_size, num_pages, window, scale, out, T, H, G, d, nullptr, 0, nullptr, s);
 }

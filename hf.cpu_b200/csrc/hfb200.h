@@ -142,6 +142,16 @@ int hfb_attention_decode(const void *q, const void *k_cache, const void *v_cache
                          int window, float scale, void *out, void *scratch, size_t scratch_bytes, int T, int H, int G,
                          int d, int *counters, int counters_len, hfb_stream s);
 
+/* The same with options of the softmax: `sinks` (float32 [H], or `zero_sink` for a score of zero), a score per head
+ * without key or value that joins the denominator once, and `slopes` (float32 [H]): slope * (query position - key
+ * position) is taken off every score. */
+int hfb_attention_decode_opt(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
+                             int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
+                             const int32_t *tile_nt, int n_tiles, int stages, int splits, int block_size, int64_t num_pages,
+                             int window, float scale, void *out, void *scratch, size_t scratch_bytes, int T, int H, int G,
+                             int d, int *counters, int counters_len, const float *sinks, int zero_sink, const float *slopes,
+                             hfb_stream s);
+
 /* Attention of prompt portions on tcgen05 (S and PV accumulators in TMEM, K and V gathered page by page with
  * TMA): bfloat16, head_dim 128, block sizes 8..128 that divide 128.  Tiles hold at most 128 / (H/G) tokens. */
 int hfb_attention_tc(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
@@ -155,6 +165,13 @@ int hfb_attention_tc2(const void *q, const void *k_cache, const void *v_cache, c
                       int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
                       const int32_t *tile_nt, int n_tiles, int block_size, int64_t num_pages, int window, float scale,
                       void *out, int T, int H, int G, int d, hfb_stream s);
+
+/* ... with the options of hfb_attention_decode_opt. */
+int hfb_attention_tc2_opt(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
+                          int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
+                          const int32_t *tile_nt, int n_tiles, int block_size, int64_t num_pages, int window, float scale,
+                          void *out, int T, int H, int G, int d, const float *sinks, int zero_sink, const float *slopes,
+                          hfb_stream s);
 
 /* out[t, f] = silu(g) * u with g = gu[t, f], u = gu[t, F + f], or, interleaved, g = gu[t, 2f], u = gu[t, 2f + 1] */
 int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, int interleaved, hfb_stream s);

@@ -133,19 +133,37 @@ __global__ void conv_carry_kernel(const float *x, int splits, int taps, float *c
 // d entries in registers (entry i of the column sits in lane i / R).  q and k rows are [Hq heads of d] (head h reads head
 // h / (H / Hq)), a (the decays) [H heads of d], v and o [H heads of dv]; every row pointer comes with its own stride so
 // that the operands may be slices of wider product outputs.  beta_logit [T, beta_stride]: u = sigmoid(beta_logit) (v -
-// S^T k); NULL: u = v.  The next token's operands are fetched while the current one is worked on.
+// S^T k); NULL: u = v.
+//
+// The walk along the tokens is a chain of dependent steps, so what a step waits for decides the kernel's speed: the
+// operands of `ct` tokens at a time (the head's q, k and a rows, the block's slice of v, beta) come into shared memory by
+// cp.async, two chunks deep, and a step reads them from there instead of from global memory.  A row of d values lies in
+// shared memory as L groups of R with 4 floats between the groups, so that the lanes of a column read their 16-byte
+// pieces from different banks.  Only the state's update is a chain from token to token; a lane's piece of o = S^T q
+// goes to shared memory as it is, and the pieces of a chunk's tokens are summed (in lane order) and stored when the
+// chunk is done.
+__device__ __forceinline__ void cp_async4(float *dst, const float *src)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int R, int L>
 __global__ void __launch_bounds__(256)
 linear_scan_kernel(const float *q, int q_stride, const float *k, int k_stride, const float *v, int v_stride,
                    const float *a, int a_stride, const float *beta_logit, int beta_stride, float q_scale, float *state,
                    size_t slot_stride, const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, float *o,
-                   int o_stride, int H, int Hq, int d, int dv, int *err)
+                   int o_stride, int H, int Hq, int d, int dv, int ct, int *err)
 {
-    pdl_entry();
-    pdl_sync_small();
-    constexpr int COLS = 256 / L;
+    pdl_wait();                                      // (a long kernel: its successor is released when the walk is done)
+    extern __shared__ float4 scan_smem4[];
+    float *smem = (float *)scan_smem4;
+    constexpr int COLS = 256 / L, RS = L * (R + 4);              // columns of a block; floats of a padded row
+    const int stage_floats = (ct * (3 * RS + COLS + 1) + 3) & ~3;
+    float *ob = smem + 2 * stage_floats;                         // [ct][256]: every lane's piece of o
     const int seq = blockIdx.x, h = blockIdx.y;
-    const int col = blockIdx.z * COLS + threadIdx.x / L, part = threadIdx.x % L;
+    const int lcol = threadIdx.x / L, col = blockIdx.z * COLS + lcol, part = threadIdx.x % L;
     const int slot = seq_slots[seq];
     if (slot < 0 || slot >= n_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
     const int t0 = cu_tokens[seq], t1 = cu_tokens[seq + 1];
@@ -154,50 +172,89 @@ linear_scan_kernel(const float *q, int q_stride, const float *k, int k_stride, c
     const int hq = h / (H / Hq);
     const int i0 = part * R;
     float *sp = state + (size_t)slot * slot_stride + ((size_t)h * dv + cj) * d + i0;
-    float S[R], qa[R], ka[R], aa[R], qn[R], kn[R], an[R];
+    float S[R];
 #pragma unroll
     for (int r = 0; r < R; r++) S[r] = (i0 + r < d) ? sp[r] : 0.f;
-    float vn = 0.f, bn = 0.f;
-    auto fetch = [&](int t) {
-        const float *qp = q + (size_t)t * q_stride + hq * d + i0, *kp = k + (size_t)t * k_stride + hq * d + i0;
-        const float *ap = a + (size_t)t * a_stride + h * d + i0;
+    bool in[R];
 #pragma unroll
-        for (int r = 0; r < R; r++) {
-            const bool in = i0 + r < d;
-            qn[r] = in ? qp[r] : 0.f;
-            kn[r] = in ? kp[r] : 0.f;
-            an[r] = in ? ap[r] : 0.f;
+    for (int r = 0; r < R; r++) in[r] = i0 + r < d;
+
+    auto issue = [&](int c) {
+        float *st = smem + (c & 1) * stage_floats;
+        const int tb = t0 + c * ct, n = min(ct, t1 - tb);
+        for (int idx = threadIdx.x; idx < n * d; idx += 256) {
+            const int tt = idx / d, i = idx - tt * d;
+            float *dst = st + tt * RS + (i / R) * (R + 4) + i % R;
+            cp_async4(dst, q + (size_t)(tb + tt) * q_stride + hq * d + i);
+            cp_async4(dst + ct * RS, k + (size_t)(tb + tt) * k_stride + hq * d + i);
+            cp_async4(dst + 2 * ct * RS, a + (size_t)(tb + tt) * a_stride + h * d + i);
         }
-        vn = v[(size_t)t * v_stride + h * dv + cj];
-        bn = beta_logit ? beta_logit[(size_t)t * beta_stride + h] : 0.f;
+        float *sv = st + 3 * ct * RS;
+        for (int idx = threadIdx.x; idx < n * COLS; idx += 256) {
+            const int tt = idx / COLS, c_ = idx % COLS, gc = blockIdx.z * COLS + c_;
+            cp_async4(sv + idx, v + (size_t)(tb + tt) * v_stride + h * dv + (gc < dv ? gc : 0));
+        }
+        if (beta_logit)
+            for (int idx = threadIdx.x; idx < n; idx += 256) cp_async4(sv + ct * COLS + idx, beta_logit + (size_t)(tb + idx) * beta_stride + h);
+        cp_async_commit();
     };
-    if (t0 < t1) fetch(t0);
-    for (int t = t0; t < t1; t++) {
+
+    const int n_chunks = (t1 - t0 + ct - 1) / ct;
+    if (n_chunks > 0) issue(0);
+    for (int c = 0; c < n_chunks; c++) {
+        if (c + 1 < n_chunks) { issue(c + 1); cp_async_wait<1>(); } else cp_async_wait<0>();
+        __syncthreads();
+        const float *st = smem + (c & 1) * stage_floats;
+        const int tb = t0 + c * ct, n = min(ct, t1 - tb);
+#pragma unroll 2
+        for (int tt = 0; tt < n; tt++) {
+            float qa[R], ka[R], aa[R];
+            const float4 *rq = (const float4 *)(st + tt * RS + part * (R + 4));
+            const float4 *rk = (const float4 *)(st + (ct + tt) * RS + part * (R + 4));
+            const float4 *ra = (const float4 *)(st + (2 * ct + tt) * RS + part * (R + 4));
 #pragma unroll
-        for (int r = 0; r < R; r++) { qa[r] = qn[r]; ka[r] = kn[r]; aa[r] = an[r]; }
-        const float vt = vn, bt = bn;
-        if (t + 1 < t1) fetch(t + 1);
-        float u = vt;
-        if (beta_logit) {
-            float dot = 0.f;
+            for (int r4 = 0; r4 < R / 4; r4++) {
+                const float4 x = rq[r4], y = rk[r4], z = ra[r4];
+                qa[4 * r4] = x.x; qa[4 * r4 + 1] = x.y; qa[4 * r4 + 2] = x.z; qa[4 * r4 + 3] = x.w;
+                ka[4 * r4] = y.x; ka[4 * r4 + 1] = y.y; ka[4 * r4 + 2] = y.z; ka[4 * r4 + 3] = y.w;
+                aa[4 * r4] = z.x; aa[4 * r4 + 1] = z.y; aa[4 * r4 + 2] = z.z; aa[4 * r4 + 3] = z.w;
+            }
 #pragma unroll
-            for (int r = 0; r < R; r++) { S[r] *= aa[r]; dot = fmaf(S[r], ka[r], dot); }
+            for (int r = 0; r < R; r++) {                         // beyond d the shared memory holds nothing
+                qa[r] = in[r] ? qa[r] : 0.f; ka[r] = in[r] ? ka[r] : 0.f; aa[r] = in[r] ? aa[r] : 0.f;
+            }
+            const float vt = st[3 * ct * RS + tt * COLS + lcol];
+            float u = vt;
+            if (beta_logit) {
+                const float gate = sigmoid_f(st[3 * ct * RS + ct * COLS + tt]);
+                float dot4[4] = {0.f, 0.f, 0.f, 0.f};                // four chains, summed in a fixed order
 #pragma unroll
-            for (int m = L / 2; m > 0; m >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
-            u = sigmoid_f(bt) * (vt - dot);
+                for (int r = 0; r < R; r++) { S[r] *= aa[r]; dot4[r & 3] = fmaf(S[r], ka[r], dot4[r & 3]); }
+                float dot = (dot4[0] + dot4[1]) + (dot4[2] + dot4[3]);
 #pragma unroll
-            for (int r = 0; r < R; r++) S[r] = fmaf(ka[r], u, S[r]);
-        } else {
+                for (int m = L / 2; m > 0; m >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
+                u = gate * (vt - dot);
 #pragma unroll
-            for (int r = 0; r < R; r++) S[r] = fmaf(aa[r], S[r], ka[r] * u);
+                for (int r = 0; r < R; r++) S[r] = fmaf(ka[r], u, S[r]);
+            } else {
+#pragma unroll
+                for (int r = 0; r < R; r++) S[r] = fmaf(aa[r], S[r], ka[r] * u);
+            }
+            float acc4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < R; r++) acc4[r & 3] = fmaf(S[r], qa[r], acc4[r & 3]);
+            ob[tt * 256 + threadIdx.x] = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
         }
-        float acc = 0.f;
+        __syncthreads();                                         // the stage is free for the chunk after the next
+        for (int idx = threadIdx.x; idx < n * COLS; idx += 256) {
+            const int tt = idx / COLS, c_ = idx % COLS, gc = blockIdx.z * COLS + c_;
+            float acc = 0.f;
 #pragma unroll
-        for (int r = 0; r < R; r++) acc = fmaf(S[r], qa[r], acc);
-#pragma unroll
-        for (int m = L / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
-        if (live && part == 0) o[(size_t)t * o_stride + h * dv + col] = acc * q_scale;
+            for (int l = 0; l < L; l++) acc += ob[tt * 256 + c_ * L + l];
+            if (gc < dv) o[(size_t)(tb + tt) * o_stride + h * dv + gc] = acc * q_scale;
+        }
     }
+    pdl_trigger();
     if (live) {
 #pragma unroll
         for (int r = 0; r < R; r++)
@@ -286,10 +343,17 @@ extern "C" int hfb_linear_scan(const float *q, int q_stride, const float *k, int
         return fail(HFB_EINVAL, "linear_scan: bad arguments (H=%d Hq=%d d=%d dv=%d)", H, Hq, d, dv);
     if (d > REC_MAX_D) return fail(HFB_ENOTSUP, "linear_scan: key heads above %d are not supported", REC_MAX_D);
     if (H > 65535) return fail(HFB_ENOTSUP, "linear_scan: %d heads exceed the grid limit", H);
-#define HFB_SCAN(R, L) \
-    g_launch_err = launch_pdl(linear_scan_kernel<R, L>, dim3(S, H, (dv + 256 / L - 1) / (256 / L)), dim3(256), 0, (cudaStream_t)s, q, q_stride, \
-        k, k_stride, v, v_stride, a, a_stride, beta_logit, beta_stride, q_scale, state, (size_t)slot_stride, cu_tokens, seq_slots, n_slots, \
-        o, o_stride, H, Hq, d, dv, error_word())
+    // tokens per chunk: two stages of ct * (3 padded rows + the columns' values + beta) floats and the lanes' pieces of o
+    // (ct * 256 floats) within 46 KB, 16 at most
+#define HFB_SCAN(R, L) do { \
+        const int per_token = (3 * L * (R + 4) + 256 / L + 1) * 4; \
+        int ct = (46 * 1024 - 32) / (2 * per_token + 1024); \
+        ct = ct < 1 ? 1 : (ct > 16 ? 16 : ct); \
+        const size_t smem = 2 * (size_t)(((ct * (per_token / 4)) + 3) & ~3) * 4 + (size_t)ct * 1024; \
+        g_launch_err = launch_pdl(linear_scan_kernel<R, L>, dim3(S, H, (dv + 256 / L - 1) / (256 / L)), dim3(256), smem, (cudaStream_t)s, q, q_stride, \
+            k, k_stride, v, v_stride, a, a_stride, beta_logit, beta_stride, q_scale, state, (size_t)slot_stride, cu_tokens, seq_slots, n_slots, \
+            o, o_stride, H, Hq, d, dv, ct, error_word()); \
+    } while (0)
     if (d <= 32) HFB_SCAN(4, 8);
     else if (d <= 64) HFB_SCAN(8, 8);
     else if (d <= 128) HFB_SCAN(16, 8);

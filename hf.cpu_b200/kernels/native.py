@@ -153,8 +153,10 @@ class NativeBackend:
     def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tile_arrays, dv=None, sinks=None,
                         zero_sink=False, slopes=None):
         self._on_gpu(q, k_cache, v_cache, meta.block_table, ctx.token_seq, ctx.positions, out, sinks, slopes)
-        if sinks is not None or zero_sink or slopes is not None:
-            tile_arrays = None                # a sink or a distance bias: the plain kernel has them
+        # a sink or a distance bias: the two-tile tensor-core kernel (prompt portions of 64 tokens and more), the decode
+        # kernel and the plain kernel have them
+        opts = sinks is not None or zero_sink or slopes is not None
+        opt_args = (_p(sinks), c_int(1 if zero_sink else 0), _p(slopes))
         T = q.shape[0]
         dv = d if dv is None else dv
         v_row = dv
@@ -180,16 +182,16 @@ class NativeBackend:
                 # items 22.7 against 17.9 us, 116 items 32.3 against 37.9 us; 40 over 8: 88 items 23.0 against 26.7 us).
                 # Head size 64 has this form only and always takes it (16 items: 14.6 us against 17.7 us of mma.sync)
                 tiling = tiles(H // G, 16) if self.attention_tc2 else None
-                enough = self.tc2_min_rounds * self.sm_count if d == 128 else 0
+                enough = self.tc2_min_rounds * self.sm_count if d == 128 and not opts else 0
                 if tiling is not None and tiling[3] * G >= enough:
                     tile_seq, tile_t0, tile_nt, n_tiles = tiling
-                    self._check(self.lib.hfb_attention_tc2(
+                    self._check(self.lib.hfb_attention_tc2_opt(
                         _p(q), _p(k_cache), _p(v_cache), _p(meta.block_table), c_int(meta.max_blocks), _p(ctx.positions),
                         _p(tile_seq), _p(tile_t0), _p(tile_nt), c_int(n_tiles), c_int(meta.block_size),
                         c_int64(k_cache.shape[0]), c_int(window), c_float(scale), _p(out), c_int(T), c_int(H), c_int(G),
-                        c_int(d), self._stream()), "attention_tc2")
+                        c_int(d), *opt_args, self._stream()), "attention_tc2")
                     return
-                tiling = tiles(H // G, 8) if d == 128 else None      # tiles of 128 rows, as the 8-warp kernel's
+                tiling = tiles(H // G, 8) if d == 128 and not opts else None      # tiles of 128 rows, as the 8-warp kernel's
                 if tiling is not None:
                     tile_seq, tile_t0, tile_nt, n_tiles = tiling
                     self._check(self.lib.hfb_attention_tc(
@@ -202,8 +204,8 @@ class NativeBackend:
             # tokens; smaller pages take the 4-warp kernel with one token a tile
             decode_tma = decode and meta.block_size >= 8
             warps = 4
-            tiling = tiles(H // G, 1 if decode_tma else warps)
-            if tiling is None and not decode:
+            tiling = tiles(H // G, 1 if decode_tma else warps) if decode_tma or not opts else None
+            if tiling is None and not decode and not opts:
                 warps = 8
                 tiling = tiles(H // G, 8)
             if tiling is not None:
@@ -228,12 +230,12 @@ class NativeBackend:
                         if self._counters is None or self._counters.device != q.device:
                             self._counters = torch.zeros(4096, dtype=torch.int32, device=q.device)
                         counters = self._counters
-                    self._check(self.lib.hfb_attention_decode(
+                    self._check(self.lib.hfb_attention_decode_opt(
                         _p(q), _p(k_cache), _p(v_cache), _p(meta.block_table), c_int(meta.max_blocks), _p(ctx.positions),
                         _p(tile_seq), _p(tile_t0), _p(tile_nt), c_int(n_tiles), c_int(stages), c_int(splits),
                         c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window), c_float(scale), _p(out),
                         _p(scratch), ctypes.c_size_t(need), c_int(T), c_int(H), c_int(G), c_int(d), _p(counters),
-                        c_int(counters.numel() if counters is not None else 0), self._stream()), "attention_decode")
+                        c_int(counters.numel() if counters is not None else 0), *opt_args, self._stream()), "attention_decode")
                     if splits > 1 and counters is None:
                         self.launches += 1
                     return
