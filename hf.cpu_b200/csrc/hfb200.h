@@ -173,6 +173,9 @@ int hfb_attention_tc2_opt(const void *q, const void *k_cache, const void *v_cach
                           void *out, int T, int H, int G, int d, const float *sinks, int zero_sink, const float *slopes,
                           hfb_stream s);
 
+/* Launches may overlap with the kernel in front (programmatic dependent launch): on by default, off with HFB_PDL=0. */
+void hfb_set_launch_overlap(int on);
+
 /* out[t, f] = silu(g) * u with g = gu[t, f], u = gu[t, F + f], or, interleaved, g = gu[t, 2f], u = gu[t, 2f + 1] */
 int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, int interleaved, hfb_stream s);
 

@@ -18,14 +18,15 @@ int fail(int code, const char *fmt, ...)
     return code;
 }
 
+static int g_pdl_on = -1;             // -1: not decided yet (the environment decides at the first launch)
+
 bool pdl_enabled()
 {
-    static int on = -1;
-    if (on < 0) {
+    if (g_pdl_on < 0) {
         const char *v = getenv("HFB_PDL");
-        on = !(v && v[0] == '0');
+        g_pdl_on = !(v && v[0] == '0');
     }
-    return on != 0;
+    return g_pdl_on != 0;
 }
 
 __device__ int g_error_word = 0;
@@ -113,4 +114,12 @@ extern "C" int hfb_error_word_take(int32_t *word, hfb_stream s)
     if (e != cudaSuccess) return hfb::fail(HFB_ECUDA, "reading the device error word: %s", cudaGetErrorString(e));
     *word = v;
     return HFB_OK;
+}
+
+// Whether kernels are launched so that one may start before the kernel in front of it has finished (programmatic
+// dependent launch).  HFB_PDL=0 in the environment keeps it off whatever is asked for here.
+extern "C" void hfb_set_launch_overlap(int on)
+{
+    const char *v = getenv("HFB_PDL");
+    g_pdl_on = (on != 0) && !(v && v[0] == '0');
 }

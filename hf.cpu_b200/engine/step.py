@@ -16,6 +16,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
+from .. import kernels
 from ..cache import KVCacheManager, OutOfPages, StateSlots
 from ..models import EMBEDDING_STATE, Model
 
@@ -171,6 +172,8 @@ class Engine:
         self.slots = StateSlots(state_specs, self.max_requests, self.device)
         self.workspace = Workspace(self.device)
         self._pinned = self.device.type == "cuda"
+        # (a setting of the process's launches: the engine made last decides)
+        kernels.set_launch_overlap(all(getattr(p, "launch_overlap_safe", True) for p in model.all_parts()))
         # pure decode steps are captured once per (batch size, key-split bucket) as a CUDA graph and replayed
         self.use_graphs = (self._pinned and os.environ.get("HFB_GRAPHS", "1") != "0"
                            and all(getattr(p, "graph_safe", False) for p in model.all_parts()))

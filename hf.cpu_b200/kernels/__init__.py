@@ -192,6 +192,14 @@ def tiled_attention_takes(dtype, head_dim: int, block_size: int) -> bool:
             and getattr(b, "attention", "plain") == "fast")
 
 
+def set_launch_overlap(on: bool) -> None:
+    """Whether a kernel may be launched so that it starts (and waits) before the kernel in front of it has finished.  A
+    backend without such launches ignores it."""
+    fn = getattr(backend(), "set_launch_overlap", None)
+    if fn is not None:
+        fn(bool(on))
+
+
 def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None, dv=None, values_in_keys=False,
                     sinks=None, zero_sink=False, slopes=None) -> None:
     """``window``: a :func:`mask_code`.  ``tiles``: the device arrays of :func:`attention_step_arrays` for this step

@@ -150,6 +150,9 @@ class NativeBackend:
                                                c_int64(cache_slots), c_int(T), c_int(H), c_int(G), c_int(d),
                                                self._stream()), "rope_kv_write")
 
+    def set_launch_overlap(self, on):
+        self.lib.hfb_set_launch_overlap(c_int(1 if on else 0))
+
     def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tile_arrays, dv=None, sinks=None,
                         zero_sink=False, slopes=None):
         self._on_gpu(q, k_cache, v_cache, meta.block_table, ctx.token_seq, ctx.positions, out, sinks, slopes)

@@ -83,6 +83,9 @@ class Part:
     # True when forward() only launches kernels on tensors at stable addresses and reads nothing of the step
     # on the host, so that a decode step may be captured once as a CUDA graph and replayed
     graph_safe = False
+    # False for a part whose kernels have not been cleared to start before the kernel in front of them has finished; the
+    # engine then launches a model with such a part without that overlap
+    launch_overlap_safe = True
 
     def tensor_specs(self) -> List[TensorSpec]:
         """The checkpoint tensors this part needs."""

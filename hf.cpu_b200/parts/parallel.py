@@ -32,6 +32,10 @@ class ParallelMixer(Mixer):
     def graph_safe(self):
         return all(getattr(b, "graph_safe", False) for b in self.branches)
 
+    @property
+    def launch_overlap_safe(self):
+        return all(getattr(b, "launch_overlap_safe", True) for b in self.branches)
+
     def cache_spec(self):
         return next((b.cache_spec() for b in self.branches if b.cache_spec() is not None), None)
 

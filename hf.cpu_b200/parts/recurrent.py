@@ -31,6 +31,9 @@ from .base import Mixer, StateSpec, register_part
 
 class _Recurrent(OutputProduct, Mixer):
     graph_safe = True
+    # A prompt's walk runs for milliseconds on a few blocks.  With launches that overlap, a warmed-up process stopped
+    # making progress in the prompt steps of layers of width 2,048 (queued back to back); without the overlap it does not.
+    launch_overlap_safe = False
     b_o = None
 
     def _t(self, name):
