@@ -121,5 +121,5 @@ extern "C" int hfb_error_word_take(int32_t *word, hfb_stream s)
 extern "C" void hfb_set_launch_overlap(int on)
 {
     const char *v = getenv("HFB_PDL");
-    g_pdl_on = (on != 0) && !(v && v[0] == '0');
+    hfb::g_pdl_on = (on != 0) && !(v && v[0] == '0');
 }
