@@ -6,7 +6,8 @@ from .qwen2 import Qwen2Config
 from .manapel import ManapelConfig
 from .peludra import PeludraConfig
 from .mokisun import MokisunConfig
+from .silupel import SilupelConfig
 
 __all__ = ["ConfigError", "UnsupportedError", "ModelConfig", "ModelPlan", "PartSpec", "LayerSpec",
-           "ScheduleEntry", "Qwen2Config", "ManapelConfig", "PeludraConfig", "MokisunConfig", "config_from_dict", "config_from_gguf", "load_config",
+           "ScheduleEntry", "Qwen2Config", "ManapelConfig", "PeludraConfig", "MokisunConfig", "SilupelConfig", "config_from_dict", "config_from_gguf", "load_config",
            "register_architecture", "unregister_architecture", "known_architectures"]

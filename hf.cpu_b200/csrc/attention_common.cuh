@@ -60,6 +60,10 @@ struct AttnParams {
     // taken off every score
     const float *sinks, *slopes;
     int zero_sink;
+    // options of the score (the decode kernel): a factor per head [H] on the scaled score, and a cap,
+    // score <- softcap * tanh(score / softcap), applied after the factors and before bias and softmax (0: none)
+    const float *head_scales = nullptr;
+    float softcap = 0.f, scale = 0.f;   // scale: the plain factor (scale_log2 without log2(e)), for the capped form
 };
 
 // Byte offset of 16-byte chunk `c` of row `row` in a tile whose rows hold D bf16 (D = 64 or 128).

@@ -150,6 +150,13 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         // the distance bias in the exponent's base 2; rows beyond the tile's tokens have none
         const float sl0 = (p.slopes && v0) ? p.slopes[g * r + row0 % r] * 1.4426950408889634f : 0.f;
         const float sl1 = (p.slopes && v1) ? p.slopes[g * r + row1 % r] * 1.4426950408889634f : 0.f;
+        // the factor on a row's raw scores (with the head's own factor), and with a cap the argument's factor instead
+        const float hs0 = (p.head_scales && v0) ? p.head_scales[g * r + row0 % r] : 1.f;
+        const float hs1 = (p.head_scales && v1) ? p.head_scales[g * r + row1 % r] : 1.f;
+        const bool capped = p.softcap > 0.f;
+        const float f0 = capped ? p.scale * hs0 / p.softcap : p.scale_log2 * hs0;
+        const float f1 = capped ? p.scale * hs1 / p.softcap : p.scale_log2 * hs1;
+        const float cap2 = p.softcap * 1.4426950408889634f;
         const int kbase = warp * 16, mi = lane >> 3;
         // the 8 keys whose rows this lane names to ldmatrix lie in one page (pages hold 8 keys or more)
         const int bs = p.block_size;
@@ -177,7 +184,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             for (int i = 0; i < 2; i++) {
 #pragma unroll
                 for (int e = 0; e < 2; e++) {
-                    float a = sc[i][e] * p.scale_log2, b = sc[i][2 + e] * p.scale_log2;
+                    float a = sc[i][e] * f0, b = sc[i][2 + e] * f1;
+                    if (capped) { a = cap2 * tanh_fast(a); b = cap2 * tanh_fast(b); }
                     const int key = kt * ABN + kbase + i * 8 + (lane & 3) * 2 + e;
                     if (p.slopes) {
                         a = fmaf(sl0, (float)(key - pos0), a);
@@ -447,7 +455,8 @@ extern "C" int hfb_attention_decode_opt(const void *q, const void *k_cache, cons
                                     int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
                                     const int32_t *tile_nt, int n_tiles, int stages, int splits, int block_size,
                                     int64_t num_pages, int window, float scale, void *out, void *scratch, size_t scratch_bytes,
-                                    int T, int H, int G, int d, int *counters, int counters_len, const float *sinks, int zero_sink, const float *slopes, hfb_stream s)
+                                    int T, int H, int G, int d, int *counters, int counters_len, const float *sinks, int zero_sink, const float *slopes,
+                                    const float *head_scales, float softcap, hfb_stream s)
 {
     if (n_tiles <= 0) return HFB_OK;
     if (d != 64 && d != 128) return fail(HFB_ENOTSUP, "attention_decode: head_dim %d (64 and 128 only)", d);
@@ -473,6 +482,7 @@ extern "C" int hfb_attention_decode_opt(const void *q, const void *k_cache, cons
     p.max_blocks = max_blocks; p.block_size = block_size; p.window = window; p.H = H; p.G = G; p.splits = splits;
     p.num_pages = num_pages; p.scale_log2 = scale * 1.4426950408889634f;
     p.sinks = sinks; p.slopes = slopes; p.zero_sink = zero_sink;
+    p.head_scales = head_scales; p.softcap = softcap > 0.f ? softcap : 0.f; p.scale = scale;
     p.counters = (splits > 1 && splits <= 64 && counters && counters_len >= n_tiles * G) ? counters : nullptr;
     cudaStream_t st = (cudaStream_t)s;
     if (one_map) rc = d == 128 ? launch_decode_stages<128, true>(stages, mk, mv, p, slots, n_tiles, st)
@@ -491,5 +501,5 @@ extern "C" int hfb_attention_decode(const void *q, const void *k_cache, const vo
 {
     return hfb_attention_decode_opt(q, k_cache, v_cache, block_table, max_blocks, positions, tile_seq, tile_t0, tile_nt, n_tiles,
                                     stages, splits, block_size, num_pages, window, scale, out, scratch, scratch_bytes, T, H, G, d,
-                                    counters, counters_len, nullptr, 0, nullptr, s);
+                                    counters, counters_len, nullptr, 0, nullptr, nullptr, 0.f, s);
 }

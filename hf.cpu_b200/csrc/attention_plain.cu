@@ -12,6 +12,8 @@
 // Two options of the softmax: a sink per head, a score without key or value that joins the denominator once
 // (p_j = exp(s_j) / (exp(sink) + sum exp(s_j)); `sinks` [H] float32, learned, or `zero_sink` for a sink of score 0,
 // which adds one to the denominator), and a bias linear in the distance, s_j -= slopes[h] * (pos - j).
+// Two options of the score: a factor per head, s_j *= head_scales[h], and a cap, s_j <- softcap * tanh(s_j / softcap)
+// (after the factors, before the bias and the softmax; softcap <= 0: none).
 #include "common.cuh"
 
 static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
@@ -27,7 +29,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int32_t *block_table, int max_blocks,
                        const int32_t *token_seq, const int32_t *positions, int block_size, long long num_pages,
                        int window, float scale, T *out, int H, int G, int d, int dv, int v_row, const float *sinks, int zero_sink,
-                       const float *slopes, int *err)
+                       const float *slopes, const float *head_scales, float softcap, int *err)
 {
     pdl_sync();
     int t = blockIdx.x, h = blockIdx.y;
@@ -45,6 +47,8 @@ attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int
     __syncthreads();
 
     const float slope = slopes ? slopes[h] : 0.f;
+    if (head_scales) scale *= head_scales[h];
+    const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
     float m = -INFINITY, l = 0.f, acc[MAX_D_PER_LANE];
 #pragma unroll
     for (int i = 0; i < MAX_D_PER_LANE; i++) acc[i] = 0.f;
@@ -62,6 +66,7 @@ attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int
             if (c < d) dot = fmaf(sq[c], to_f32(k_cache[base + c]), dot);
         }
         dot = warp_sum(dot) * scale;
+        if (softcap > 0.f) dot = softcap * tanhf(dot * inv_cap);
         if (slopes) dot -= slope * (float)(pos - j);
         float m_new = fmaxf(m, dot);
         float corr = expf(m - m_new);            // exp(-inf) = 0 on the first key
@@ -113,7 +118,7 @@ extern "C" int hfb_attention_plain(const void *q, const void *k_cache, const voi
                                    const int32_t *block_table, int max_blocks, const int32_t *token_seq,
                                    const int32_t *positions, int block_size, int64_t num_pages, int window,
                                    float scale, void *out, int T, int H, int G, int d, int dv, int v_row, const float *sinks,
-                                   int zero_sink, const float *slopes, hfb_stream s)
+                                   int zero_sink, const float *slopes, const float *head_scales, float softcap, hfb_stream s)
 {
     if (T <= 0) return HFB_OK;
     if (!valid_dt(dt) || H <= 0 || G <= 0 || H % G || block_size <= 0 || max_blocks <= 0 || v_row < dv)
@@ -125,7 +130,7 @@ extern "C" int hfb_attention_plain(const void *q, const void *k_cache, const voi
     const bool small = d <= 256 && dv <= 256;
 #define HFB_PLAIN_ATT(TY, L) \
     g_launch_err = launch_pdl(attention_plain_kernel<TY, L>, dim3(grid), dim3(ATT_WARPS * 32), 0, (cudaStream_t)s, (const TY *)q, (const TY *)k_cache, \
-        (const TY *)v_cache, block_table, max_blocks, token_seq, positions, block_size, num_pages, window, scale, (TY *)out, H, G, d, dv, v_row, sinks, zero_sink, slopes, error_word())
+        (const TY *)v_cache, block_table, max_blocks, token_seq, positions, block_size, num_pages, window, scale, (TY *)out, H, G, d, dv, v_row, sinks, zero_sink, slopes, head_scales, softcap, error_word())
     if (dt == HFB_F32) { if (small) HFB_PLAIN_ATT(float, 8); else HFB_PLAIN_ATT(float, MAX_D_PER_LANE); }
     else { if (small) HFB_PLAIN_ATT(__nv_bfloat16, 8); else HFB_PLAIN_ATT(__nv_bfloat16, MAX_D_PER_LANE); }
 #undef HFB_PLAIN_ATT

@@ -48,6 +48,10 @@ struct AttnTc2Params {
     // that joins the denominator once; slopes [H]: slope * (query position - key position) is taken off every score
     const float *sinks, *slopes;
     int zero_sink;
+    // options of the score: a factor per head [H] on the scaled score, and a cap, score <- softcap * tanh(score / softcap),
+    // after the factors and before bias and softmax (0: none); scale is scale_log2 without log2(e)
+    const float *head_scales;
+    float softcap, scale;
 };
 
 __device__ __forceinline__ float u_ex2(float x)
@@ -286,6 +290,9 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
             const int lo = mask_lo(pos, p.window);
             // the distance bias in the exponent's base 2 (rows beyond the tile's tokens have none)
             const float slope2 = (p.slopes && valid) ? p.slopes[it.g * r + hl] * 1.4426950408889634f : 0.f;
+            const float hscale = (p.head_scales && valid) ? p.head_scales[it.g * r + hl] : 1.f;
+            const bool capped = p.softcap > 0.f;
+            const float cap_in = capped ? p.scale * hscale / p.softcap : 0.f, cap2 = p.softcap * 1.4426950408889634f;
             float m_ref = -INFINITY, l = 0.f;        // the maximum the exponentials refer to, and the sum in its scale
             for (int j = 0; j < n_mine && ok; j++) {
                 const uint32_t ph = (g_mine + j) & 1;
@@ -303,12 +310,20 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                 // 128 dependent operations is not hidden by the other warp)
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                 float sc = p.scale_log2;
-                if (p.slopes) {
-                    // with a bias the scores are scaled and biased in place first, and the factor below is one
+                if (capped) {
+                    // with a cap the scores are finished in place (factors, tanh, bias), and the factor below is one
                     const float b0 = slope2 * (float)(key0 - pos);
 #pragma unroll
                     for (int c = 0; c < 128; c++)
-                        sv[c] = __float_as_uint(fmaf(__uint_as_float(sv[c]), p.scale_log2, fmaf(slope2, (float)c, b0)));
+                        sv[c] = __float_as_uint(fmaf(cap2, tanh_fast(__uint_as_float(sv[c]) * cap_in), fmaf(slope2, (float)c, b0)));
+                    sc = 1.f;
+                } else if (p.slopes || p.head_scales) {
+                    // with a bias or a head's own factor (of either sign) the scores are scaled and biased in place
+                    // first, and the factor below is one
+                    const float b0 = slope2 * (float)(key0 - pos), k = p.scale_log2 * hscale;
+#pragma unroll
+                    for (int c = 0; c < 128; c++)
+                        sv[c] = __float_as_uint(fmaf(__uint_as_float(sv[c]), k, fmaf(slope2, (float)c, b0)));
                     sc = 1.f;
                 }
                 // rows beyond the tile's tokens (their queries are zeros, nothing of them is written) go with the
@@ -446,7 +461,7 @@ extern "C" int hfb_attention_tc2_opt(const void *q, const void *k_cache, const v
                                  int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
                                  const int32_t *tile_nt, int n_tiles, int block_size, int64_t num_pages, int window,
                                  float scale, void *out, int T, int H, int G, int d, const float *sinks, int zero_sink, const float *slopes,
-                                     hfb_stream s)
+                                     const float *head_scales, float softcap, hfb_stream s)
 {
     if (n_tiles <= 0) return HFB_OK;
     if (d != 64 && d != 128) return fail(HFB_ENOTSUP, "attention_tc2: head_dim %d (64 and 128 only)", d);
@@ -470,6 +485,7 @@ extern "C" int hfb_attention_tc2_opt(const void *q, const void *k_cache, const v
     p.n_tiles = n_tiles;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.sinks = sinks; p.slopes = slopes; p.zero_sink = zero_sink;
+    p.head_scales = head_scales; p.softcap = softcap > 0.f ? softcap : 0.f; p.scale = scale;
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -484,5 +500,5 @@ extern "C" int hfb_attention_tc2(const void *q, const void *k_cache, const void 
                                  float scale, void *out, int T, int H, int G, int d, hfb_stream s)
 {
     return hfb_attention_tc2_opt(q, k_cache, v_cache, block_table, max_blocks, positions, tile_seq, tile_t0, tile_nt, n_tiles,
-                                 block_size, num_pages, window, scale, out, T, H, G, d, nullptr, 0, nullptr, s);
+                                 block_size, num_pages, window, scale, out, T, H, G, d, nullptr, 0, nullptr, nullptr, 0.f, s);
 }

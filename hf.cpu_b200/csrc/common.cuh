@@ -140,6 +140,16 @@ __device__ __forceinline__ void rope_pair(float a, float b, float c, float s, fl
     hi = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
 }
 
+// tanh from one exponential and one reciprocal of the special-function unit: 1 - 2 / (2^(2 x log2 e) + 1); absolute
+// error of a few 1e-7 over the whole range (the ends saturate to -1 and 1 through 2 / 1 and 2 / inf).
+__device__ __forceinline__ float tanh_fast(float x)
+{
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.8853900817779268f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+    return fmaf(-2.0f, r, 1.0f);
+}
+
 // The first key a query at `pos` sees, from the one number that names a layer's mask: window > 0, itself and the
 // window - 1 positions before it; window < 0, the keys of its own chunk of -window positions, chunks counted from
 // position 0 of the request; 0, every key.  Never decreases as pos grows, which the tiled kernels rely on.

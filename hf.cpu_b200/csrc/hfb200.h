@@ -110,11 +110,14 @@ int hfb_rope_kv_write(const void *qkv, int dt, const float *cos_sin, int n_rot, 
  * sees the keys of its own chunk); 0, lo = 0.  Keys [.., G, d], values [.., G, dv] with rows v_row elements apart
  * (dv; or d with v_cache == k_cache, when a value is the first dv elements of its key), out [T, H dv].  Head sizes up
  * to 640. */
+/* Options of the score that the plain kernel, the two-tile tensor-core kernel and the decode kernel take: `head_scales`
+ * (float32 [H], or NULL): the scaled score of head h is multiplied by head_scales[h]; `softcap` > 0: the score becomes
+ * softcap * tanh(score / softcap), after the factors and before any bias and the softmax. */
 int hfb_attention_plain(const void *q, const void *k_cache, const void *v_cache, int dt,
                         const int32_t *block_table, int max_blocks, const int32_t *token_seq,
                         const int32_t *positions, int block_size, int64_t num_pages, int window, float scale,
                         void *out, int T, int H, int G, int d, int dv, int v_row, const float *sinks, int zero_sink,
-                        const float *slopes, hfb_stream s);
+                        const float *slopes, const float *head_scales, float softcap, hfb_stream s);
 
 /* The same for bfloat16 with head_dim 64 or 128 and a block size that divides 64, tiled, on tensor cores.
  * Tiles (tile_seq, tile_t0 = first token index, tile_nt = tokens) cover the step's tokens; a tile holds at
@@ -150,7 +153,7 @@ int hfb_attention_decode_opt(const void *q, const void *k_cache, const void *v_c
                              const int32_t *tile_nt, int n_tiles, int stages, int splits, int block_size, int64_t num_pages,
                              int window, float scale, void *out, void *scratch, size_t scratch_bytes, int T, int H, int G,
                              int d, int *counters, int counters_len, const float *sinks, int zero_sink, const float *slopes,
-                             hfb_stream s);
+                             const float *head_scales, float softcap, hfb_stream s);
 
 /* Attention of prompt portions on tcgen05 (S and PV accumulators in TMEM, K and V gathered page by page with
  * TMA): bfloat16, head_dim 128, block sizes 8..128 that divide 128.  Tiles hold at most 128 / (H/G) tokens. */
@@ -171,7 +174,7 @@ int hfb_attention_tc2_opt(const void *q, const void *k_cache, const void *v_cach
                           int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
                           const int32_t *tile_nt, int n_tiles, int block_size, int64_t num_pages, int window, float scale,
                           void *out, int T, int H, int G, int d, const float *sinks, int zero_sink, const float *slopes,
-                          hfb_stream s);
+                          const float *head_scales, float softcap, hfb_stream s);
 
 /* Launches may overlap with the kernel in front (programmatic dependent launch): on by default, off with HFB_PDL=0. */
 void hfb_set_launch_overlap(int on);
@@ -313,6 +316,28 @@ int hfb_linear_scan(const float *q, int q_stride, const float *k, int k_stride, 
                     int n_slots, int S, float *o, int o_stride, int H, int Hq, int d, int dv, hfb_stream s);
 int hfb_gate_norm(const float *o, const void *w, int w_dt, float eps, const float *g, int g_splits, int g_stride,
                   int g_col0, int gate, void *out, int out_dt, int T, int H, int dv, hfb_stream s);
+
+/* minGRU over a step's tokens: row = `splits` float32 planes [T, 3 W] of [update gate | candidate | output gate] sums;
+ * z = sigmoid(a + bz), u = b + bx, cand = u >= 0 ? u + 1/2 : sigmoid(u), S <- (1 - z) S + z cand, out = S silu(g); S [W]
+ * float32 per request in its slot of `state` (rows slot_stride apart). */
+int hfb_mingru_scan(const float *row, int splits, const void *bz, const void *bx, int b_dt, float *state, int64_t slot_stride,
+                    const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, int S, void *out, int out_dt, int T, int W,
+                    hfb_stream s);
+
+/* Layer norm of rows of the float32 stream: (x - mean) / sqrt(var + eps) * w (center = 1) or x / sqrt(mean(x^2) + eps) * w
+ * (center = 0), w float32 [E]; out[r] = norm(x[rows ? rows[r] : r]) for N rows, x having n_src rows. */
+int hfb_layernorm(const float *x, const float *w, float eps, int center, const int32_t *rows, int n_src, void *out, int out_dt,
+                  int N, int E, hfb_stream s);
+/* The same norm with the token shift behind it: out[t] = h_t + (h_(t-1) - h_t) * mu, h = norm(x), h_(t-1) from the step's
+ * previous row or, for a request's first token of the step, from its slot of `state` (float32, rows slot_stride apart),
+ * which then receives the h of the request's last token of the step. */
+int hfb_layernorm_shift(const float *x, const float *w, const float *mu, float eps, int center, float *state, int64_t slot_stride,
+                        const int32_t *token_seq, const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, void *out,
+                        int out_dt, int T, int E, hfb_stream s);
+/* out = a * sigmoid(g) (gate 1) or a * silu(g) (gate 0); g: `splits` float32 planes [T, g_stride] from column g_col0 on,
+ * plus `bias` (float32 [C]) where given; a and out [T, C] of type dt. */
+int hfb_gate_mul(const void *a, int dt, const float *g, int splits, int g_stride, int g_col0, const float *bias, int gate, void *out,
+                 int T, int C, hfb_stream s);
 
 /* out[m] = index of the first maximum of logits[m, :] */
 int hfb_argmax(const float *logits, int32_t *out, int M, int V, hfb_stream s);

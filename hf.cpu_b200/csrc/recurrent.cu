@@ -295,6 +295,78 @@ static unsigned rec_blocks(size_t total)
     return (unsigned)(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
 }
 
+
+// minGRU: a gated recurrence per channel whose gates read the current token only.  With a = row[.., c] (update gate's
+// sum), b = row[.., W + c] (candidate's sum), g = row[.., 2 W + c] (output gate's sum), each the sum of `splits` float32
+// planes [T, 3 W], and biases on the first two:
+//     z = sigmoid(a + bz);  u = b + bx;  cand = u >= 0 ? u + 1/2 : sigmoid(u);  S <- (1 - z) S + z cand;
+//     out = S * silu(g)
+// S [W] float32 per request lives in its state slot.  A block takes MG_CH channels of one request.  Its warps first
+// compute, for a chunk of MG_CT tokens, everything that does not depend on S (z, z * cand, silu(g): three exponentials
+// a token and channel) into shared memory, in parallel over tokens; then the first warp walks the chunk, one channel a
+// lane, two multiply-adds a token, while the other warps already work on the next chunk (two buffers).  The walk is
+// the same sequence of operations whatever the step's cutting, so a position's result does not depend on it.
+constexpr int MG_CH = 32, MG_CT = 32, MG_WARPS = 8;
+
+template <typename TO>
+__global__ void __launch_bounds__(MG_WARPS * 32)
+mingru_scan_kernel(const float *row, int splits, const void *bz, const void *bx, int b_dt, float *state, size_t slot_stride,
+                   const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, TO *out, int T, int W, int *err)
+{
+    pdl_entry();
+    pdl_sync_small();
+    __shared__ float s_z[2][MG_CT][MG_CH], s_b[2][MG_CT][MG_CH], s_g[2][MG_CT][MG_CH];
+    const int seq = blockIdx.y, c0 = blockIdx.x * MG_CH;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = c0 + lane;
+    const bool live = c < W;
+    const int slot = seq_slots[seq];
+    if (slot < 0 || slot >= n_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
+    const int t0 = cu_tokens[seq], n = cu_tokens[seq + 1] - t0;
+    const size_t C3 = 3 * (size_t)W, plane = (size_t)T * C3;
+    const float vbz = (live && bz) ? load_any(bz, b_dt, c) : 0.f, vbx = (live && bx) ? load_any(bx, b_dt, c) : 0.f;
+    float S = (warp == 0 && live) ? state[(size_t)slot * slot_stride + c] : 0.f;
+    const int chunks = (n + MG_CT - 1) / MG_CT;
+
+    auto fill = [&](int k, int first, int stride) {
+        // tokens k * MG_CT + first, + stride, ... of the request's share of the step
+        const int buf = k & 1;
+        for (int j = first; j < MG_CT; j += stride) {
+            const int i = k * MG_CT + j;
+            if (i >= n || !live) continue;
+            const float *p = row + (size_t)(t0 + i) * C3 + c;
+            float a = 0.f, b = 0.f, g = 0.f;
+            for (int s = 0; s < splits; s++) {
+                a += p[(size_t)s * plane]; b += p[(size_t)s * plane + W]; g += p[(size_t)s * plane + 2 * (size_t)W];
+            }
+            const float z = sigmoid_f(a + vbz), u = b + vbx;
+            const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+            s_z[buf][j][lane] = z;
+            s_b[buf][j][lane] = z * cand;
+            s_g[buf][j][lane] = g * sigmoid_f(g);
+        }
+    };
+
+    fill(0, warp, MG_WARPS);
+    __syncthreads();
+    for (int k = 0; k < chunks; k++) {
+        if (warp == 0) {
+            const int buf = k & 1, m = min(MG_CT, n - k * MG_CT);
+            if (live) {
+                TO *o = out + (size_t)(t0 + k * MG_CT) * W + c;
+                for (int j = 0; j < m; j++) {
+                    S = fmaf(1.0f - s_z[buf][j][lane], S, s_b[buf][j][lane]);
+                    o[(size_t)j * W] = from_f32<TO>(S * s_g[buf][j][lane]);
+                }
+            }
+        } else if (k + 1 < chunks) {
+            fill(k + 1, warp - 1, MG_WARPS - 1);
+        }
+        __syncthreads();
+    }
+    if (warp == 0 && live) state[(size_t)slot * slot_stride + c] = S;
+}
+
 }  // namespace hfb
 
 using namespace hfb;
@@ -378,4 +450,23 @@ extern "C" int hfb_gate_norm(const float *o, const void *w, int w_dt, float eps,
         g_launch_err = launch_pdl(gate_norm_kernel<__nv_bfloat16>, dim3(T, hb), dim3(REC_WARPS * 32), 0, (cudaStream_t)s, o, w, w_dt, eps, g,
                                   g_splits, g_stride, g_col0, gate, (__nv_bfloat16 *)out, T, H, dv);
     return check_pdl_launch(g_launch_err, "gate_norm");
+}
+
+extern "C" int hfb_mingru_scan(const float *row, int splits, const void *bz, const void *bx, int b_dt, float *state, int64_t slot_stride,
+                               const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, int S, void *out, int out_dt, int T,
+                               int W, hfb_stream s)
+{
+    if (S <= 0 || T <= 0) return HFB_OK;
+    if (!row || !state || !cu_tokens || !seq_slots || !out || !valid_dt(out_dt) || splits < 1 || W <= 0 || slot_stride < W ||
+        ((bz || bx) && !valid_dt(b_dt)))
+        return fail(HFB_EINVAL, "mingru_scan: bad arguments (W=%d)", W);
+    if (S > 65535) return fail(HFB_ENOTSUP, "mingru_scan: %d requests exceed the grid limit", S);
+    const dim3 grid((W + MG_CH - 1) / MG_CH, S);
+    if (out_dt == HFB_F32)
+        g_launch_err = launch_pdl(mingru_scan_kernel<float>, grid, dim3(MG_WARPS * 32), 0, (cudaStream_t)s, row, splits, bz, bx, b_dt, state,
+                                  (size_t)slot_stride, cu_tokens, seq_slots, n_slots, (float *)out, T, W, error_word());
+    else
+        g_launch_err = launch_pdl(mingru_scan_kernel<__nv_bfloat16>, grid, dim3(MG_WARPS * 32), 0, (cudaStream_t)s, row, splits, bz, bx, b_dt,
+                                  state, (size_t)slot_stride, cu_tokens, seq_slots, n_slots, (__nv_bfloat16 *)out, T, W, error_word());
+    return check_pdl_launch(g_launch_err, "mingru_scan");
 }

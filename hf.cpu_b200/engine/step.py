@@ -18,7 +18,7 @@ import torch
 
 from .. import kernels
 from ..cache import KVCacheManager, OutOfPages, StateSlots
-from ..models import EMBEDDING_STATE, Model
+from ..models import EMBEDDING_STATE, Model, block_state_key
 
 
 @dataclass
@@ -155,6 +155,8 @@ class Engine:
                 cache_specs[i] = mixer.cache_spec()
             if mixer.state_spec() is not None:
                 state_specs[i] = mixer.state_spec()
+            if model.layers[e.layer].block.state_spec() is not None:
+                state_specs[block_state_key(i)] = model.layers[e.layer].block.state_spec()
         if model.embedding.state_spec() is not None:
             state_specs[EMBEDDING_STATE] = model.embedding.state_spec()
         for i, e in enumerate(plan.schedule):

@@ -201,20 +201,28 @@ def set_launch_overlap(on: bool) -> None:
 
 
 def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None, dv=None, values_in_keys=False,
-                    sinks=None, zero_sink=False, slopes=None) -> None:
+                    sinks=None, zero_sink=False, slopes=None, head_scales=None, softcap: float = 0.0) -> None:
     """``window``: a :func:`mask_code`.  ``tiles``: the device arrays of :func:`attention_step_arrays` for this step
     (without them only the plain kernel runs).  ``dv``: the size of a value head where it is not ``d``; ``out`` is then
     [T, H * dv].  ``values_in_keys``: there is no array of values, a value is the first ``dv`` elements of its key.
     ``sinks`` (float32 [H]): a score per head that joins the softmax's denominator once and has no value; ``zero_sink``:
     such a score of 0 for every head (one is added to the denominator).  ``slopes`` (float32 [H]): slope * (query
-    position - key position) is taken off every score."""
+    position - key position) is taken off every score.  ``head_scales`` (float32 [H]): the scaled score of head h is
+    multiplied by head_scales[h]; ``softcap`` > 0: the score becomes softcap * tanh(score / softcap), after the factors and
+    before the bias and the softmax."""
     dv = d if dv is None else int(dv)
     extra = {}
+    if head_scales is not None or softcap:
+        _need(head_scales is None or (head_scales.shape == (H,) and head_scales.dtype == torch.float32),
+              "attention: head_scales are float32 [H]")
+        _need(softcap >= 0, "attention: softcap must be positive (0: none)")
     if sinks is not None or zero_sink or slopes is not None:
         _need(sinks is None or (sinks.shape == (H,) and sinks.dtype == torch.float32), "attention: sinks are float32 [H]")
         _need(slopes is None or (slopes.shape == (H,) and slopes.dtype == torch.float32), "attention: slopes are float32 [H]")
         _need(not (zero_sink and sinks is not None), "attention: a learned sink or a sink of zero, not both")
         extra = {"sinks": sinks, "zero_sink": bool(zero_sink), "slopes": slopes}
+    if head_scales is not None or softcap:
+        extra.update(head_scales=head_scales, softcap=float(softcap))
     if values_in_keys:
         _need(0 < dv <= d <= MAX_LATENT_ROW and v_cache is None, "attention: values inside keys need dv <= d <= %d" % MAX_LATENT_ROW)
         _need(q.shape[1] == H * d and out.shape == (q.shape[0], H * dv) and k_cache.shape[2:] == (G, d), "attention: shape mismatch")
@@ -649,6 +657,53 @@ def gate_norm(o, w, eps: float, g, g_splits: int, g_stride: int, g_col0: int, ga
     _need(g.dtype == torch.float32 and g.numel() >= g_splits * T * g_stride and g_col0 + H * dv <= g_stride and gate in ("silu", "sigmoid"),
           "gate_norm: g float32 [splits, T, stride]; gate silu or sigmoid")
     backend().gate_norm(o, w, float(eps), g, int(g_splits), int(g_stride), int(g_col0), 0 if gate == "silu" else 1, out, int(H), int(dv))
+
+
+# ---- layer norm, token shift, gates, minGRU ----------------------------------------------------------------------
+def layernorm(x, w, eps: float, out, rows: Optional[torch.Tensor] = None, center: bool = True) -> None:
+    """out = (x - mean) / sqrt(var + eps) * w over rows of the float32 stream (``center`` False: x / sqrt(mean(x^2) + eps)
+    * w); ``w`` float32 [E]; with ``rows`` (int32) only those rows, in that order."""
+    _need(x.dtype == torch.float32 and x.dim() == 2, "layernorm: x must be float32 [N, E]")
+    _need(w.shape == (x.shape[1],) and w.dtype == torch.float32 and out.shape[1] == x.shape[1], "layernorm: the weight is float32 [E]")
+    _need(rows is None or (rows.dtype == torch.int32 and rows.shape[0] == out.shape[0]), "layernorm: rows must be int32 [M]")
+    _need(rows is not None or out.shape[0] == x.shape[0], "layernorm: row count mismatch")
+    backend().layernorm(x, w, float(eps), bool(center), out, rows)
+
+
+def norm_shift(x, w, eps: float, center: bool, mu, state, ctx, out) -> None:
+    """The norm of :func:`layernorm` with the token shift behind it: out[t] = h_t + (h_(t-1) - h_t) * mu, h = norm(x); the
+    previous token's h comes from the step's previous row or, for a request's first token of the step, from the request's
+    row of ``state`` (float32 [slots, E]), which then receives the h of the request's last token of the step."""
+    T, E = x.shape
+    _need(x.dtype == torch.float32 and out.shape == (T, E), "norm_shift: x must be float32 [T, E] and out [T, E]")
+    _need(w.shape == (E,) and mu.shape == (E,) and w.dtype == mu.dtype == torch.float32, "norm_shift: weight and shift are float32 [E]")
+    _need(state is not None and state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] == E,
+          "norm_shift: the state is float32 [slots, E]")
+    backend().norm_shift(x, w, float(eps), bool(center), mu, state, ctx, out)
+
+
+def gate_mul(a, g, g_splits: int, g_stride: int, g_col0: int, bias, gate: str, out) -> None:
+    """out = a * sigmoid(g) or a * silu(g); ``g`` is the float32 sums of a product ([splits, T, g_stride], read from column
+    ``g_col0`` on) plus ``bias`` (float32 [C]) where there is one; ``a`` and ``out`` [T, C] in the run's type."""
+    _need(gate in ("silu", "sigmoid"), "gate_mul: gate is 'silu' or 'sigmoid'")
+    _need(a.shape == out.shape and a.dtype == out.dtype and a.dim() == 2, "gate_mul: a and out must agree")
+    _need(g.dtype == torch.float32 and g_col0 + a.shape[1] <= g_stride and g.numel() >= g_splits * a.shape[0] * g_stride,
+          "gate_mul: the gate's sums are float32 [splits, T, g_stride]")
+    _need(bias is None or (bias.shape == (a.shape[1],) and bias.dtype == torch.float32), "gate_mul: the bias is float32 [C]")
+    backend().gate_mul(a, g, int(g_splits), int(g_stride), int(g_col0), bias, gate, out)
+
+
+def mingru_scan(row, splits: int, bias_z, bias_x, state, ctx, out, W: int) -> None:
+    """minGRU over the step's tokens, request by request from each request's state: ``row`` is the float32 sums of the
+    product [update gate | candidate | output gate] ([splits, T, 3 W]); z = sigmoid(a + bias_z), u = b + bias_x,
+    cand = u + 1/2 where u >= 0 and sigmoid(u) where u < 0, S <- (1 - z) S + z cand, out = S * silu(g).  ``state`` float32
+    [slots, W] holds S between steps; ``out`` [T, W] in the run's type."""
+    _need(row.dtype == torch.float32 and row.numel() >= splits * out.shape[0] * 3 * W and out.shape[1] == W,
+          "mingru_scan: rows are float32 [splits, T, 3 W]")
+    _need(state is not None and state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] == W,
+          "mingru_scan: the state is float32 [slots, W]")
+    _need(all(b is None or b.shape == (W,) for b in (bias_z, bias_x)), "mingru_scan: biases are [W]")
+    backend().mingru_scan(row, int(splits), bias_z, bias_x, state, ctx, out, int(W))
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

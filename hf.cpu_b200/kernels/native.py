@@ -154,12 +154,13 @@ class NativeBackend:
         self.lib.hfb_set_launch_overlap(c_int(1 if on else 0))
 
     def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tile_arrays, dv=None, sinks=None,
-                        zero_sink=False, slopes=None):
-        self._on_gpu(q, k_cache, v_cache, meta.block_table, ctx.token_seq, ctx.positions, out, sinks, slopes)
+                        zero_sink=False, slopes=None, head_scales=None, softcap=0.0):
+        self._on_gpu(q, k_cache, v_cache, meta.block_table, ctx.token_seq, ctx.positions, out, sinks, slopes, head_scales)
         # a sink or a distance bias: the two-tile tensor-core kernel (prompt portions of 64 tokens and more), the decode
         # kernel and the plain kernel have them
-        opts = sinks is not None or zero_sink or slopes is not None
-        opt_args = (_p(sinks), c_int(1 if zero_sink else 0), _p(slopes))
+        # ... and a factor per head on the scores and a tanh cap
+        opts = sinks is not None or zero_sink or slopes is not None or head_scales is not None or softcap > 0
+        opt_args = (_p(sinks), c_int(1 if zero_sink else 0), _p(slopes), _p(head_scales), c_float(softcap))
         T = q.shape[0]
         dv = d if dv is None else dv
         v_row = dv
@@ -255,8 +256,7 @@ class NativeBackend:
                                                  c_int(meta.max_blocks), _p(ctx.token_seq), _p(ctx.positions),
                                                  c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window),
                                                  c_float(scale), _p(out), c_int(T), c_int(H), c_int(G), c_int(d), c_int(dv),
-                                                 c_int(v_row), _p(sinks), c_int(1 if zero_sink else 0), _p(slopes),
-                                                 self._stream()), "attention")
+                                                 c_int(v_row), *opt_args, self._stream()), "attention")
 
     def swiglu(self, gu, out, interleaved):
         self._on_gpu(gu, out)
@@ -557,6 +557,34 @@ class NativeBackend:
         self._check(self.lib.hfb_gate_norm(_p(o), _p(w), c_int(_dt(w)), c_float(eps), _p(g), c_int(g_splits), c_int(g_stride),
                                            c_int(g_col0), c_int(gate), _p(out), c_int(_dt(out)), c_int(o.shape[0]), c_int(H), c_int(dv),
                                            self._stream()), "gate_norm")
+
+    def layernorm(self, x, w, eps, center, out, rows):
+        self._on_gpu(x, w, out, rows)
+        self._check(self.lib.hfb_layernorm(_p(x), _p(w), c_float(eps), c_int(1 if center else 0), _p(rows), c_int(x.shape[0]), _p(out),
+                                           c_int(_dt(out)), c_int(out.shape[0]), c_int(x.shape[1]), self._stream()), "layernorm")
+
+    def norm_shift(self, x, w, eps, center, mu, state, ctx, out):
+        self._on_gpu(x, w, mu, out, ctx.token_seq, ctx.cu_tokens, ctx.seq_slots)
+        self._check(self.lib.hfb_layernorm_shift(
+            _p(x), _p(w), _p(mu), c_float(eps), c_int(1 if center else 0), _p(state), c_int64(state.stride(0)), _p(ctx.token_seq),
+            _p(ctx.cu_tokens), _p(ctx.seq_slots), c_int(state.shape[0]), _p(out), c_int(_dt(out)), c_int(x.shape[0]), c_int(x.shape[1]),
+            self._stream()), "layernorm_shift")
+
+    def gate_mul(self, a, g, g_splits, g_stride, g_col0, bias, gate, out):
+        self._on_gpu(a, bias, out)
+        self._check(self.lib.hfb_gate_mul(_p(a), c_int(_dt(a)), _p(g), c_int(g_splits), c_int(g_stride), c_int(g_col0), _p(bias),
+                                          c_int(1 if gate == "sigmoid" else 0), _p(out), c_int(a.shape[0]), c_int(a.shape[1]),
+                                          self._stream()), "gate_mul")
+
+    def mingru_scan(self, row, splits, bias_z, bias_x, state, ctx, out, W):
+        self._on_gpu(bias_z, bias_x, out, ctx.cu_tokens, ctx.seq_slots)
+        b_dt = _dt(bias_z) if bias_z is not None else (_dt(bias_x) if bias_x is not None else 0)
+        if bias_z is not None and bias_x is not None and bias_z.dtype != bias_x.dtype:
+            raise KernelError("mingru_scan: the two biases must have one type")
+        self._check(self.lib.hfb_mingru_scan(_p(row), c_int(splits), _p(bias_z), _p(bias_x), c_int(b_dt), _p(state),
+                                             c_int64(state.stride(0)), _p(ctx.cu_tokens), _p(ctx.seq_slots), c_int(state.shape[0]),
+                                             c_int(ctx.num_seqs), _p(out), c_int(_dt(out)), c_int(out.shape[0]), c_int(W),
+                                             self._stream()), "mingru_scan")
 
     def moe_group(self, ids, experts, order, tile_expert, tile_p0, tile_n, n_tiles, tile):
         self._on_gpu(ids, order, tile_expert, tile_p0, tile_n, n_tiles)

@@ -21,6 +21,12 @@ from ..weights import RandomSource, TensorSpec, load_tensors
 EMBEDDING_STATE = "embedding"        # the key of the embedding's per-request state among the schedule entries' states
 
 
+def block_state_key(entry: int):
+    """The key of a block's own per-request state (a token shift's previous row) for schedule entry ``entry``; a layer
+    that runs more than once has one per run."""
+    return ("block", entry)
+
+
 @dataclass
 class Layer:
     block: object
@@ -134,6 +140,8 @@ class Model:
                     extra["next_block"] = self.layers[schedule[i + 1].layer].block
             else:
                 next_norm = self.final_norm if getattr(ctx, "logits_for_all", False) else None
+            if layer.block.state_spec() is not None:
+                extra["block_state"] = ctx.entry_state(block_state_key(i))
             xn = layer.block.forward(ctx, x, layer.norm1, layer.mixer, layer.norm2, layer.ffn,
                                      ctx.entry_cache(owner), ctx.entry_state(i), e.cache_of is None,
                                      xn_ready=xn, next_norm=next_norm, **extra)

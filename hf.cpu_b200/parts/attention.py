@@ -24,6 +24,10 @@ that has no key, no value and no scale; "zero" does the same with a score of 0 (
 ``distance_slope_exp`` = c: ``2^(-c (h + 1) / H) * (i - j)`` is taken off the score of query i and key j in head h.
 ``values_are_keys``: the layer has no value projection, a key as it is cached also serves as its value (one array of
 rows in the cache).  A rotary encoding with the pairing "interleaved" turns the dimensions (2i, 2i + 1) together.
+``head_scale_tensor`` names a stored number per head by which the head's scaled scores are multiplied; ``softcap`` = c > 0
+turns a score s into ``c tanh(s / c)`` (after the factors, before the softmax).  ``out_gate`` = {"tensor": name, "kind":
+"sigmoid" | "silu"}: the concatenated heads' outputs are multiplied element by element by ``kind(W_gate h)`` before the
+output product, ``W_gate`` [H * v_head_dim, hidden] reading the same input as the other projections.
 """
 from __future__ import annotations
 
@@ -84,7 +88,7 @@ class PagedAttention(OutputProduct, Mixer):
                  positions=None, names=None, scale=None, v_head_dim=None, qk_norm_eps=None, own_kv: bool = True,
                  bias_suffix: str = ".bias", weight_suffix: str = ".weight", qk_norm_weights=None, chunk: int = 0,
                  v_mix=None, v_mix_tensor: str = "vmix", sink=None, sink_tensor: str = "sink", distance_slope_exp=None,
-                 values_are_keys: bool = False, **_):
+                 values_are_keys: bool = False, head_scale_tensor=None, softcap=None, out_gate=None, **_):
         self.E, self.H, self.G, self.d = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
         if self.H % self.G:
             raise UnsupportedError(f"unsupported attention geometry: {self.H} heads over {self.G} key/value heads")
@@ -107,8 +111,15 @@ class PagedAttention(OutputProduct, Mixer):
             raise UnsupportedError("a layer without values of its own cannot mix them")
         if qk_norm_weights and self.qk_norm_eps is None:
             raise UnsupportedError("weights on the query and key norm need that norm (qk_norm_eps)")
+        self.softcap = float(softcap) if softcap else 0.0
+        if self.softcap < 0:
+            raise UnsupportedError("attention: the cap on the scores must be positive")
+        self.gate_kind = (out_gate or {}).get("kind", "sigmoid") if out_gate else None
+        if self.gate_kind not in (None, "sigmoid", "silu"):
+            raise UnsupportedError(f"attention: output gate '{self.gate_kind}' is not known (sigmoid, silu)")
         self.general = (self.qk_norm_eps is not None or self.dv != self.d or not self.own_kv or self.v_mix is not None
                         or self.values_are_keys or self.sink is not None or self.slope_exp is not None
+                        or head_scale_tensor is not None or self.softcap > 0 or out_gate is not None
                         or getattr((positions or {}).get(position), "pairing", "half") != "half")
         if self.general:
             if not (0 < self.d <= kernels.MAX_HEAD_DIM and 0 < self.dv <= kernels.MAX_HEAD_DIM):
@@ -130,7 +141,10 @@ class PagedAttention(OutputProduct, Mixer):
             raise UnsupportedError("qk_norm_weights names one weight for q and one for k")
         self.v_mix_name = f"{prefix}.{v_mix_tensor}" if self.v_mix else None
         self.sink_name = f"{prefix}.{sink_tensor}" if self.sink == "learned" else None
-        self.sinks = self.slopes = None          # float32 [H]
+        self.head_scale_name = f"{prefix}.{head_scale_tensor}" if head_scale_tensor else None
+        self.gate_name = f"{prefix}.{out_gate['tensor']}" if out_gate else None
+        self.sinks = self.slopes = self.head_scales = None          # float32 [H]
+        self.w_gate = None
         self.scale = 1.0 / math.sqrt(self.d) if scale is None else float(scale)
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
         self.norm_w = None              # (q weight, k weight), float32
@@ -181,6 +195,10 @@ class PagedAttention(OutputProduct, Mixer):
             s.append(TensorSpec(self.v_mix_name, (), init="half"))       # the first layer's is stored too, and unused
         if self.sink_name:
             s.append(TensorSpec(self.sink_name, (self.H,)))
+        if self.head_scale_name:
+            s.append(TensorSpec(self.head_scale_name, (self.H,), init="norm"))
+        if self.gate_name:
+            s.append(TensorSpec(self.gate_name + self.wsuf, (self.OD, self.E)))
         return s
 
     def bind(self, tensors, run_dtype, device):
@@ -198,12 +216,16 @@ class PagedAttention(OutputProduct, Mixer):
             self.v_lambda = float(lam.to(torch.float32).reshape(-1)[0].item()) if self.v_mix == "later" else 0.0
         if self.sink_name:
             self.sinks = tensors[self.sink_name].to(torch.float32).contiguous()
+        if self.head_scale_name:
+            self.head_scales = tensors[self.head_scale_name].to(torch.float32).contiguous()
+        if self.gate_name:
+            self.w_gate = tensors[self.gate_name + self.wsuf].contiguous()
         if self.slope_exp is not None:
             h = torch.arange(1, self.H + 1, dtype=torch.float64)
             self.slopes = torch.pow(2.0, -self.slope_exp * h / self.H).to(torch.float32).to(device)
 
     def weight_bytes(self):
-        return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.b_qkv, self.w_o, self.b_o)
+        return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.b_qkv, self.w_o, self.b_o, self.w_gate)
                    if w is not None)
 
     def flops(self, q_lens, kv_lens):
@@ -216,7 +238,8 @@ class PagedAttention(OutputProduct, Mixer):
             elif self.chunk > 0:
                 for_all = sum((m - n + i) % self.chunk + 1 for i in range(n))
             seen += for_all
-        return 2.0 * T * (self.w_qkv.numel() + self.w_o.numel()) + 2.0 * (self.QD + self.OD) * seen
+        gate = self.w_gate.numel() if self.w_gate is not None else 0
+        return 2.0 * T * (self.w_qkv.numel() + self.w_o.numel() + gate) + 2.0 * (self.QD + self.OD) * seen
 
     def _attend(self, ctx, xn, cache, write_cache):
         T = xn.shape[0]
@@ -250,7 +273,13 @@ class PagedAttention(OutputProduct, Mixer):
             kernels.paged_attention(q, cache.k, None if self.values_are_keys else cache.v, meta, ctx, self.H, self.G, self.d,
                                     self.mask, self.scale, att, tiles=ctx.arrays(self.step_arrays_key()), dv=self.dv,
                                     values_in_keys=self.values_are_keys, sinks=self.sinks, zero_sink=self.sink == "zero",
-                                    slopes=self.slopes)
+                                    slopes=self.slopes, head_scales=self.head_scales, softcap=self.softcap)
+        if self.w_gate is not None:
+            # the gate reads the mixer's input as the projections do; its sums stay float32 up to the sigmoid
+            with kernels.phase("qkv"):
+                g, splits = kernels.product_sums(xn, self.w_gate, ctx.buf("attn_gate32", (T, self.OD), torch.float32))
+            with kernels.phase("attn"):
+                kernels.gate_mul(att, g, splits, self.OD, 0, None, self.gate_kind, att)
         return att
 
 

@@ -160,6 +160,11 @@ class FeedForward(Part):
 
 
 class Block(Part):
+    def state_spec(self) -> Optional[StateSpec]:
+        """Per-request state of the block itself (beside its mixer's), handed to ``forward`` as ``block_state``; one per
+        schedule entry."""
+        return None
+
     def forward(self, ctx, x: torch.Tensor, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward,
                 cache, state, write_cache: bool, xn_ready: Optional[torch.Tensor] = None,
                 next_norm: Optional[Norm] = None) -> Optional[torch.Tensor]:

@@ -1,4 +1,5 @@
-"""Residual arrangements.  Pre-norm: ``x += mixer(norm1(x)); x += ffn(norm2(x))`` (src/model.c:580-623).
+"""Residual arrangements.  Pre-norm: ``x += mixer(norm1(x)); x += ffn(norm2(x))`` (src/model.c:580-623); with a token
+shift, the mixer reads ``h_t + (h_(t-1) - h_t) * mu`` instead of ``h_t = norm1(x_t)``.
 Norm on both sides of each sublayer: ``x += post1(mixer(norm1(x))); x += post2(ffn(norm2(x)))``, where a layer may
 have no feed-forward at all.  Hyper-connections: the stream is kept in several copies; a sublayer reads a weighted
 sum of them, and its output is written back into every copy while the copies are mixed among themselves."""
@@ -9,21 +10,48 @@ import torch
 from .. import kernels
 from ..config.base import UnsupportedError
 from ..weights.loader import TensorSpec
-from .base import Block, register_part
+from .base import Block, StateSpec, register_part
 
 
 class PreNormResidual(Block):
+    """``token_shift``: the name of a stored vector mu [hidden_size]; what the mixer reads is then moved towards the previous
+    token's normed input, ``h_t + (h_(t-1) - h_t) * mu`` (zeros before a request's first token; the previous token's h as
+    it was before its own shift).  The last h of a request is per-request state of the block, one float32 row per
+    schedule entry, so that a step may bring only the next token of a request.  The feed-forward reads ``norm2(x)`` as
+    it is."""
     graph_safe = True
 
-    def __init__(self, **_):
-        pass
+    def __init__(self, token_shift=None, hidden_size: int = 0, **_):
+        self.shift_tensor, self.E = token_shift, int(hidden_size)
+        if self.shift_tensor and self.E < 1:
+            raise UnsupportedError("a block with a token shift needs the width of the stream")
+        self.mu = None
 
-    def forward(self, ctx, x, norm1, mixer, norm2, ffn, cache, state, write_cache, xn_ready=None, next_norm=None):
-        if xn_ready is None:
+    def tensor_specs(self):
+        return [TensorSpec(self.shift_tensor, (self.E,), init="half")] if self.shift_tensor else []
+
+    def bind(self, tensors, run_dtype, device):
+        if self.shift_tensor:
+            self.mu = tensors[self.shift_tensor].to(torch.float32).contiguous()
+
+    def state_spec(self):
+        return StateSpec((self.E,)) if self.shift_tensor else None
+
+    def forward(self, ctx, x, norm1, mixer, norm2, ffn, cache, state, write_cache, xn_ready=None, next_norm=None, block_state=None):
+        if self.shift_tensor:
+            args = getattr(norm1, "shift_args", None)
+            if args is None or block_state is None:
+                raise UnsupportedError("the token shift needs a norm that offers it and the block's per-request state")
+            xn = ctx.buf("block_xn", x.shape, ctx.run_dtype)
+            with kernels.phase("glue"):
+                kernels.norm_shift(x, *args(), self.mu, block_state, ctx, xn)
+        elif xn_ready is None:
             xn = ctx.buf("block_xn", x.shape, ctx.run_dtype)
             norm1.forward(x, xn)
         else:
             xn = xn_ready
+        if self.shift_tensor:
+            next_norm = None              # the following block shifts its own normed input: nothing to hand over
         if ffn is None:
             # a layer that is a mixer only: the norm behind its product is the next block's first
             fused = getattr(mixer, "forward_then_norm", None) if next_norm is not None else None

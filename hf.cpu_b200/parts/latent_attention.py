@@ -17,8 +17,12 @@ Where the cached row has a size the tiled tensor-core attention kernels take (th
 heads), the whole row serves as the value: the rotated columns of the weighted sum are computed and not read.  Other
 sizes take the plain kernel, which reads a value as the first ``kv_rank`` elements of its key.
 
-The mask is a sliding window (``window`` > 0) or causal (0).  The rotation pairs dimensions (2i, 2i + 1) and takes its
-table from a shared position encoding (which may be scaled for long contexts).  The reference has no such layer; the
+The mask is a sliding window (``window`` > 0) or causal (0).  The rotation takes its table from a shared position
+encoding (which may be scaled for long contexts).  The kernels turn dimensions (2i, 2i + 1) together.  An encoding with
+the pairing "half" (dimension i with i + rot_dim/2) is served by them too: the rotated part enters the scores only as
+``q_rot . k_rot``, which does not change when both are permuted alike, so the rows of the two projections that make
+the rotated parts are reordered once, when the weights are bound (i -> 2i, i + rot_dim/2 -> 2i + 1), and the cache
+holds the rotated key part in that order.  The reference has no such layer; the
 nearest thing in it is the grouped attention of src/model.c:581-609.
 """
 from __future__ import annotations
@@ -50,8 +54,9 @@ class LatentAttention(OutputProduct, Mixer):
         self.rotary = (positions or {}).get(position) if position else None
         if self.dr and self.rotary is None:
             raise UnsupportedError(f"latent attention names position encoding '{position}', which the plan does not define")
-        if self.rotary is not None and (self.rotary.pairing != "interleaved" or self.rotary.n_rot != self.dr):
-            raise UnsupportedError("latent attention rotates its whole rotated part in pairs (2i, 2i + 1)")
+        if self.rotary is not None and self.rotary.n_rot != self.dr:
+            raise UnsupportedError("latent attention rotates its whole rotated part")
+        self.reorder = self.rotary is not None and self.rotary.pairing == "half"
         n = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "o": "o"}
         n.update(names or {})
         self.names = {k: f"{prefix}.{v}" for k, v in n.items()}
@@ -79,9 +84,19 @@ class LatentAttention(OutputProduct, Mixer):
         n = self.names
         # both down projections are one product: rows [query latent | key/value latent | rotated key part]
         self.w_down = fused_rows(tensors, [n["dq"], n["dkv"]], device)
+        w_uq = tensors[n["uq"]].contiguous()
+        if self.reorder:
+            # "half" pairing: the rotated parts' rows into the order the kernels rotate in
+            half = self.dr // 2
+            order = torch.stack([torch.arange(half), torch.arange(half) + half], dim=1).reshape(-1).to(self.w_down.device)
+            tail = self.w_down[self.Qr + self.R:].clone()
+            self.w_down[self.Qr + self.R:] = tail[order]
+            per_head = w_uq.reshape(self.H, self.d + self.dr, self.Qr).clone()
+            per_head[:, self.d:] = per_head[:, self.d:][:, order.to(per_head.device)]
+            w_uq = per_head.reshape(self.H * (self.d + self.dr), self.Qr).contiguous()
         self.norm_q = tensors[n["dq_norm"]].to(torch.float32).contiguous()
         self.norm_kv = tensors[n["dkv_norm"]].to(torch.float32).contiguous()
-        self.w_uq = tensors[n["uq"]].contiguous()
+        self.w_uq = w_uq
         # a head's key expansion [d, kv_rank] is applied transposed, to the query: kept as [H, kv_rank, d]
         self.w_ukt = tensors[n["uk"]].reshape(self.H, self.d, self.R).transpose(1, 2).contiguous()
         self.w_uv = tensors[n["uv"]].reshape(self.H, self.dv, self.R).contiguous()

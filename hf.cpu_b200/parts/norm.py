@@ -1,6 +1,7 @@
 """Norms.  RMSNorm: ``y_i = (x_i * rsqrt(mean(x^2) + eps)) * w_i`` (src/mathx.c:65-75, used at src/model.c:580,
 :611, :632).  Dynamic Tanh: ``y_i = tanh(alpha * x_i) * w_i + b_i`` with a learned scalar ``alpha``: element-wise,
-no mean or variance of the row is taken (the reference has no such norm)."""
+no mean or variance of the row is taken (the reference has no such norm).  Layer norm with a weight and no bias:
+``y_i = (x_i - mean) / sqrt(var + eps) * w_i``, the variance being the mean of the squared deviations (nor this one)."""
 from __future__ import annotations
 
 import torch
@@ -19,6 +20,7 @@ class RmsNorm(Norm):
     def __init__(self, size: int, eps: float, tensor: str, offset: float = 0.0, **_):
         self.size, self.eps, self.tensor, self.offset = int(size), float(eps), tensor, float(offset)
         self.weight = None
+        self._w32 = None
 
     def tensor_specs(self):
         # random weights are drawn around the value that makes the norm's factor about one
@@ -32,9 +34,43 @@ class RmsNorm(Norm):
     def fused_args(self):
         return self.weight, self.eps
 
+    def shift_args(self):
+        """(float32 weight, eps, whether the mean is taken off) for the kernel that applies a norm with a token shift
+        behind it."""
+        if self._w32 is None:
+            self._w32 = self.weight.to(torch.float32).contiguous()
+        return self._w32, self.eps, False
+
     def forward(self, x, out, rows=None):
         with kernels.phase("glue"):
             kernels.rmsnorm(x, self.weight, self.eps, out, rows)
+        return out
+
+
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * w`` with a weight and no bias.  The weight is kept in float32 (the norm is computed
+    there in both run types)."""
+    graph_safe = True
+
+    def __init__(self, size: int, eps: float, tensor: str, optional: bool = False, **_):
+        self.size, self.eps, self.tensor, self.optional = int(size), float(eps), tensor, bool(optional)
+        self.weight = None
+
+    def tensor_specs(self):
+        # ``optional``: a norm that nothing reads (the second norm of a layer without a feed-forward) may be stored or not
+        return [TensorSpec(self.tensor, (self.size,), init="norm", optional=self.optional)]
+
+    def bind(self, tensors, run_dtype, device):
+        if self.optional and self.tensor not in tensors:
+            return
+        self.weight = tensors[self.tensor].to(torch.float32).contiguous()
+
+    def shift_args(self):
+        return self.weight, self.eps, True
+
+    def forward(self, x, out, rows=None):
+        with kernels.phase("glue"):
+            kernels.layernorm(x, self.weight, self.eps, out, rows)
         return out
 
 
@@ -85,4 +121,5 @@ class DynamicTanh(Norm):
 
 
 register_part("norm", "rmsnorm", RmsNorm)
+register_part("norm", "layernorm", LayerNorm)
 register_part("norm", "dynamic_tanh", DynamicTanh)

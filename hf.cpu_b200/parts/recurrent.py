@@ -1,4 +1,5 @@
-"""Mixers that keep a matrix of fixed size per request and head instead of keys and values per token.
+"""Mixers that keep state of fixed size per request instead of keys and values per token: a matrix per head (the two
+gated linear recurrences below) or a vector (``mingru``, at the end).
 
 Both run the gated linear recurrence per head, with a state S [d, dv] that starts at zero for a new request, lives in
 float32 in the request's state slot and is carried from token to token:
@@ -216,5 +217,55 @@ class GatedDeltaRule(_Recurrent):
         return att
 
 
+class MinGru(_Recurrent):
+    """minGRU: a gated recurrence per channel whose gates read the current token only.  With h the mixer's input,
+
+        z = sigmoid(Wz h + bz);  u = Wx h + bx;  candidate = u + 1/2 where u >= 0, sigmoid(u) where u < 0;
+        S_t = (1 - z) S_(t-1) + z candidate;      out = Wo (S_t * silu(Wg h))
+
+    all of size ``width``.  S starts at zero, is float32 and lives in the request's state slot.  The three products that
+    read h are one product [z | x | g] whose float32 sums the scan kernel takes as they are (the gates, the candidate
+    and the state are float32 in both run types); the kernel stores the output product's operand."""
+
+    def __init__(self, hidden_size: int, width: int, prefix: str, names=None, **_):
+        self.E, self.W, self.prefix = int(hidden_size), int(width), prefix
+        if self.W < 1:
+            raise UnsupportedError("minGRU: the width must be positive")
+        n = {"z": "z", "x": "x", "g": "g", "o": "o", "z_bias": "z.b", "x_bias": "x.b"}
+        n.update(names or {})
+        self.nm = n
+        self.w_in = self.w_o = self.b_z = self.b_x = None
+
+    def state_spec(self):
+        return StateSpec((self.W,))
+
+    def tensor_specs(self):
+        return [TensorSpec(self._t("z"), (self.W, self.E)), TensorSpec(self._t("x"), (self.W, self.E)),
+                TensorSpec(self._t("g"), (self.W, self.E)), TensorSpec(self._t("o"), (self.E, self.W)),
+                TensorSpec(self._t("z_bias"), (self.W,)), TensorSpec(self._t("x_bias"), (self.W,))]
+
+    def bind(self, tensors, run_dtype, device):
+        self.w_in = fused_rows(tensors, [self._t(x) for x in ("z", "x", "g")], device)
+        self.w_o = tensors[self._t("o")].contiguous()
+        self.b_z, self.b_x = tensors[self._t("z_bias")].contiguous(), tensors[self._t("x_bias")].contiguous()
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_o))
+
+    def flops(self, q_lens, kv_lens):
+        T = sum(q_lens)
+        return 2.0 * T * (self.w_in.numel() + self.w_o.numel()) + 6.0 * T * self.W
+
+    def _attend(self, ctx, xn, cache, write_cache, state):
+        T = xn.shape[0]
+        with kernels.phase("qkv"):
+            row, splits = kernels.product_sums(xn, self.w_in, ctx.buf("rec_in", (T, 3 * self.W), torch.float32))
+        att = ctx.buf("rec_att", (T, self.W), xn.dtype)
+        with kernels.phase("attn"):
+            kernels.mingru_scan(row, splits, self.b_z, self.b_x, state, ctx, att, self.W)
+        return att
+
+
 register_part("mixer", "gated_linear_attention", GatedLinearAttention)
+register_part("mixer", "mingru", MinGru)
 register_part("mixer", "gated_delta_rule", GatedDeltaRule)

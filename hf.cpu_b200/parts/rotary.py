@@ -10,7 +10,10 @@ pairings; the pairing is what the kernel that rotates does with it, so a mixer t
 ``scaling`` stretches the table for contexts longer than the ``original`` one by ``factor``, frequency by frequency:
 pairs that turn more than ``fast`` times over the original length keep their frequency, pairs that turn fewer than
 ``slow`` times have it divided by ``factor``, and between the two the pair index ramps linearly from one to the other;
-cos and sin are both multiplied by ``0.1 ln(factor) + 1``.
+cos and sin are both multiplied by ``0.1 ln(factor) + 1``.  A ``scaling`` with the keys ``low`` and ``high`` instead is the
+form by wavelength: with l = 2 pi / f, a frequency stays where l < original / high, becomes f / factor where
+l > original / low, and between the two is ``(1 - s) f / factor + s f`` with ``s = (original / l - low) / (high - low)``; cos
+and sin keep their size.
 """
 from __future__ import annotations
 
@@ -32,7 +35,14 @@ class Rotary(PositionEncoding):
             raise UnsupportedError(f"rotary width {n_rot} must be even and at most head_dim {head_dim}")
         self.head_dim, self.n_rot, self.theta, self.pairing = int(head_dim), int(n_rot), float(theta), pairing
         self.scaling = dict(scaling) if scaling else None
-        if self.scaling:
+        self.by_wavelength = bool(self.scaling) and "low" in self.scaling and "high" in self.scaling
+        if self.by_wavelength:
+            for k in ("factor", "original", "low", "high"):
+                if not float(self.scaling.get(k, 0)) > 0:
+                    raise UnsupportedError(f"rotary scaling needs a positive '{k}'")
+            if not float(self.scaling["high"]) > float(self.scaling["low"]):
+                raise UnsupportedError("rotary scaling: 'high' must exceed 'low'")
+        elif self.scaling:
             for k in ("factor", "original", "fast", "slow"):
                 if not float(self.scaling.get(k, 0)) > 0:
                     raise UnsupportedError(f"rotary scaling needs a positive '{k}'")
@@ -47,6 +57,13 @@ class Rotary(PositionEncoding):
             return f, 1.0
         sc = self.scaling
         factor = float(sc["factor"])
+        if self.by_wavelength:
+            original, low, high = float(sc["original"]), float(sc["low"]), float(sc["high"])
+            wave = 2.0 * math.pi / f
+            s = ((original / wave - low) / (high - low)).clamp(0.0, 1.0)        # 0 at the long end, 1 at the short end
+            blended = (1.0 - s) * f / factor + s * f
+            out = torch.where(wave < original / high, f, torch.where(wave > original / low, f / factor, blended))
+            return out, 1.0
 
         def pair_turning(turns):          # the (fractional) pair index that makes ``turns`` turns over the original length
             return self.n_rot * math.log(float(sc["original"]) / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))

@@ -63,7 +63,7 @@ class EmuBackend:
         vf[slots[ok].long()] = x[:, H + G:][ok].to(v_cache.dtype)
 
     def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None, dv=None, sinks=None,
-                        zero_sink=False, slopes=None):
+                        zero_sink=False, slopes=None, head_scales=None, softcap=0.0):
         T = q.shape[0]
         bs = meta.block_size
         dv = d if dv is None else dv
@@ -85,6 +85,10 @@ class EmuBackend:
             for h in range(H):
                 g = h // (H // G)
                 s = (k[:, g] @ qf[t, h]) * scale
+                if head_scales is not None:
+                    s = s * head_scales[h]
+                if softcap > 0:
+                    s = softcap * torch.tanh(s / softcap)
                 if slopes is not None:
                     s = s - slopes[h] * (pos - torch.arange(lo, pos + 1, device=q.device)).float()
                 if sinks is not None or zero_sink:
@@ -350,6 +354,47 @@ class EmuBackend:
         y = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w.float()
         y = y * (gz * torch.sigmoid(gz) if gate == 0 else torch.sigmoid(gz))
         out.copy_(y.reshape(T, H * dv).to(out.dtype))
+
+    # ---- layer norm, token shift, gates, minGRU ----
+    @staticmethod
+    def _norm_rows(x, w, eps, center):
+        d = x - x.mean(-1, keepdim=True) if center else x
+        return d / torch.sqrt((d * d).mean(-1, keepdim=True) + eps) * w
+
+    def layernorm(self, x, w, eps, center, out, rows):
+        src = x if rows is None else x[rows.long()]
+        out.copy_(self._norm_rows(src, w, eps, center).to(out.dtype))
+
+    def norm_shift(self, x, w, eps, center, mu, state, ctx, out):
+        h = self._norm_rows(x, w, eps, center)
+        cu, slots = ctx.cu_tokens.tolist(), ctx.seq_slots.tolist()
+        for s in range(len(slots)):
+            a, b = cu[s], cu[s + 1]
+            before = torch.cat([state[slots[s]][None, :], h[a:b - 1]])
+            out[a:b] = (h[a:b] + (before - h[a:b]) * mu).to(out.dtype)
+            state[slots[s]] = h[b - 1]
+
+    def gate_mul(self, a, g, g_splits, g_stride, g_col0, bias, gate, out):
+        T, C = a.shape
+        z = g.reshape(-1)[:g_splits * T * g_stride].view(g_splits, T, g_stride).sum(0)[:, g_col0:g_col0 + C]
+        if bias is not None:
+            z = z + bias
+        out.copy_((a.float() * (torch.sigmoid(z) if gate == "sigmoid" else z * torch.sigmoid(z))).to(out.dtype))
+
+    def mingru_scan(self, row, splits, bias_z, bias_x, state, ctx, out, W):
+        T = out.shape[0]
+        r = row.reshape(-1)[:splits * T * 3 * W].view(splits, T, 3 * W).sum(0)
+        z = torch.sigmoid(r[:, :W] + (bias_z.float() if bias_z is not None else 0))
+        u = r[:, W:2 * W] + (bias_x.float() if bias_x is not None else 0)
+        cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+        g = r[:, 2 * W:]
+        cu, slots = ctx.cu_tokens.tolist(), ctx.seq_slots.tolist()
+        for s in range(len(slots)):
+            S = state[slots[s]].clone()
+            for t in range(cu[s], cu[s + 1]):
+                S = (1.0 - z[t]) * S + z[t] * cand[t]
+                out[t] = (S * g[t] * torch.sigmoid(g[t])).to(out.dtype)
+            state[slots[s]] = S
 
     def moe_group(self, ids, experts, order, tile_expert, tile_p0, tile_n, n_tiles, tile):
         MOE_TILE = tile
