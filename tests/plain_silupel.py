@@ -230,3 +230,12 @@ def forward(cfg, W, ids, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.copy())
     return layer_norm(x, W["final.norm"], eps) @ W["head"].T
+
+
+def greedy(cfg, W, ids, n):
+    """n tokens by arg-max, each from a whole forward pass."""
+    ids, out = list(ids), []
+    for _ in range(n):
+        out.append(int(np.argmax(forward(cfg, W, ids)[-1])))
+        ids.append(out[-1])
+    return out
