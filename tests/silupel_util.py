@@ -67,17 +67,19 @@ CONFIGS = {"odd": ODD, "wide": WIDE, "thin": THIN}
 BLOCKS = {"odd": 8, "wide": 16, "thin": 4}
 
 
-def make_folder(cfg_dict, folder, seed, dtype=torch.float32, edit=None, sharp=3.0):
+def make_folder(cfg_dict, folder, seed, dtype=torch.float32, edit=None, sharp=None):
     """A model folder with random weights whose attention is far from uniform (query and key projections scaled up), whose
     norm weights, shifts, score factors and biases are well away from their neutral values, and whose recurrence's gates
-    are spread over (0, 1).  Stored in bfloat16 the weights are smaller, so that the rounding of large intermediate values
-    does not swamp the comparison."""
+    are spread over (0, 1).  Stored in bfloat16 the weights are smaller and the scores less sharp, so that the rounding of
+    large intermediate values, amplified by eight and more layer runs, does not swamp the comparison."""
     from hfcpu_b200.config import config_from_dict
     from hfcpu_b200.models import build_model_specs
     from hfcpu_b200.weights import random_tensors, write_safetensors, weights_path
     cfg = config_from_dict(cfg_dict)
     cfg.save(folder)
     soft = dtype == torch.bfloat16
+    if sharp is None:
+        sharp = 1.5 if soft else 3.0
     tensors = random_tensors(build_model_specs(cfg), seed, torch.float32, std=0.05 if soft else 0.09)
     g = torch.Generator().manual_seed(seed)
     for name in tensors:

@@ -17,7 +17,9 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 TOL = {"float32": 2e-4, "bfloat16": 3e-2}
-SELF_TOL = {"float32": 4e-5, "bfloat16": 1.5e-2}
+# two runs of the engine against each other; in bfloat16 they take different kernels (prompt tiles, short portions, single
+# tokens), each of which is within TOL of the exact result after eight layer runs
+SELF_TOL = {"float32": 4e-5, "bfloat16": 2e-2}
 KTOL = {"float32": 3e-6, "bfloat16": 8e-3}          # one kernel's output against float64
 
 
