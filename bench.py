@@ -312,10 +312,41 @@ def mokisun_configs(z):
     return mokisun, manapel
 
 
+# ---- `--compare silupel`: the Silupel design beside the Peludra design at equal layer sizes --------------------------
+# Layer runs in threes: latent attention, minGRU, chunked attention with a cap, a factor per head and an output gate;
+# every layer with a gated feed-forward; six layers of which the last three run twice (nine runs).  The latent row
+# (kv_rank + rot_dim) is 128.  The Peludra twin has nine layers, latent attention (causal) where Silupel has latent
+# attention or minGRU and chunked attention where it has that, and an ungated feed-forward with as many weights
+# (2 F' E = 3 F E).
+SILUPEL_SIZES = {
+    "w1024_h64": dict(width=1024, heads=16, kv=4, dim=64, rot=32, q_rank=384, kv_rank=96, rot_dim=32, chunk=1024, gru=1024, ff=2736, vocab=32768),
+    "w2048_h128": dict(width=2048, heads=16, kv=4, dim=128, rot=64, q_rank=768, kv_rank=96, rot_dim=32, chunk=2048, gru=2048, ff=5464, vocab=32768),
+    "w4096_h128": dict(width=4096, heads=32, kv=8, dim=128, rot=128, q_rank=1536, kv_rank=96, rot_dim=32, chunk=2048, gru=4096, ff=10920, vocab=32768),
+}
+
+
+def silupel_configs(z):
+    lat = dict(heads=16, dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["dim"], q_rank=z["q_rank"], kv_rank=z["kv_rank"],
+               scale=(z["dim"] + z["rot_dim"]) ** -0.5, rot=dict(dims=z["rot_dim"], base=10000.0))
+    att = dict(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, mask=dict(size=z["chunk"]))
+    mlp = dict(kind="dense", ff=z["ff"])
+    kinds = (dict(type="latent_attention", mixer=lat), dict(type="mingru", mixer=dict(width=z["gru"])),
+             dict(type="attention", mixer=dict(att, softcap=30.0, rot=dict(dims=z["rot"], base=500000.0,
+                                                                           scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))))
+    silupel = dict(architecture="Silupel", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-6), max_positions=8192,
+                   layers=[dict(kinds[i % 3], mlp=mlp) for i in range(6)], loop=dict(start=3, stop=6, times=2))
+    p_mlp = dict(kind="dense", ff=(3 * z["ff"] // 2 + 7) // 8 * 8)
+    p_lat = dict(type="latent_attention", mixer=dict(lat, mask=None))
+    peludra = dict(architecture="Peludra", vocab=z["vocab"], width=z["width"], norm=dict(eps=1e-6), max_positions=8192,
+                   embedding=dict(scale=1.0),
+                   layers=[dict(dict(type="attention", mixer=att) if i % 3 == 2 else p_lat, mlp=p_mlp) for i in range(9)])
+    return silupel, peludra
+
+
 COMPARISONS = {"manapel": (COMPARE_SIZES, compare_configs), "peludra": (PELUDRA_SIZES, peludra_configs),
-               "mokisun": (MOKISUN_SIZES, mokisun_configs)}
+               "mokisun": (MOKISUN_SIZES, mokisun_configs), "silupel": (SILUPEL_SIZES, silupel_configs)}
 # the design each comparison stands beside
-TWINS = {"manapel": "qwen2", "peludra": "qwen2", "mokisun": "manapel"}
+TWINS = {"manapel": "qwen2", "peludra": "qwen2", "mokisun": "manapel", "silupel": "peludra"}
 
 
 def phase_work(model, q_len, ctx_len, batch):
@@ -347,6 +378,9 @@ def phase_work(model, q_len, ctx_len, batch):
                 el * (keys * m.row + T * m.H * (m.row + m.R + m.dv) + m.w_uv.numel()))
         else:
             kv_row = m.d if getattr(m, "values_are_keys", False) else m.d + dv
+            gate = getattr(m, "w_gate", None)          # the output gate's product, float32 sums out
+            if gate is not None:
+                add("qkv", 2.0 * T * gate.numel(), el * gate.numel() + 4 * T * gate.shape[0])
             add("qkv", 2.0 * T * m.w_qkv.numel(), el * (m.w_qkv.numel() + T * (m.E + m.w_qkv.shape[0])))
             add("attn", 2.0 * m.H * (m.d + dv) * pairs, el * (keys * m.G * kv_row + T * m.H * (m.d + dv)))
 
@@ -364,10 +398,19 @@ def phase_work(model, q_len, ctx_len, batch):
             4 * (T * (2 * G * m.d + m.H * m.d + 2 * m.H * m.dv) + 2 * batch * m.H * m.d * m.dv) + (4 + el) * T * m.H * m.dv)
         add("wo", 2.0 * T * m.w_o.numel(), el * (m.w_o.numel() + T * m.H * m.dv) + 4 * T * m.E)
 
+    def mingru(m):
+        # one product in front (float32 sums out), the walk along the tokens (three exponentials and two multiply-adds a
+        # token and channel, the state read and written once), the output product
+        add("qkv", 2.0 * T * m.w_in.numel(), el * (m.w_in.numel() + T * m.E) + 4 * T * 3 * m.W)
+        add("attn", 12.0 * T * m.W, 4 * (T * 3 * m.W + 2 * batch * m.W) + el * T * m.W)
+        add("wo", 2.0 * T * m.w_o.numel(), el * (m.w_o.numel() + T * m.W) + 4 * T * m.E)
+
     def mixer(m):
         if hasattr(m, "branches"):
             for b in m.branches:
                 mixer(b)
+        elif hasattr(m, "b_z"):
+            mingru(m)
         elif hasattr(m, "w_in"):
             recurrent(m)
         else:

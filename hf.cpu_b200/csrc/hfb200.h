@@ -334,6 +334,13 @@ int hfb_layernorm(const float *x, const float *w, float eps, int center, const i
 int hfb_layernorm_shift(const float *x, const float *w, const float *mu, float eps, int center, float *state, int64_t slot_stride,
                         const int32_t *token_seq, const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, void *out,
                         int out_dt, int T, int E, hfb_stream s);
+/* The tail of a sublayer's last product for such norms: residual[m] += sum of `splits` partial sums [splits, M, N] (+ bias),
+ * then, if xn is given, xn[m] = norm(residual[m]) (w float32 [N]); splits = 0: only the norm.  With `mu` (float32 [N]) the
+ * token shift of a step of single tokens: row m is request m, slot seq_slots[m] of `state` gives the previous h and
+ * receives this one.  Rows of up to 16,384 values. */
+int hfb_reduce_residual_layernorm(const float *partial, int splits, int M, int N, const void *bias, int bias_dt, float *residual,
+                                  const float *w, float eps, int center, const float *mu, float *state, int64_t slot_stride,
+                                  const int32_t *seq_slots, int n_slots, void *xn, int xn_dt, hfb_stream s);
 /* out = a * sigmoid(g) (gate 1) or a * silu(g) (gate 0); g: `splits` float32 planes [T, g_stride] from column g_col0 on,
  * plus `bias` (float32 [C]) where given; a and out [T, C] of type dt. */
 int hfb_gate_mul(const void *a, int dt, const float *g, int splits, int g_stride, int g_col0, const float *bias, int gate, void *out,

@@ -120,6 +120,86 @@ __global__ void gate_mul_kernel(const TA *a, const float *g, int splits, int g_s
     }
 }
 
+
+// The tail of a product that ends a sublayer, for streams normed by the norms above: residual[m] += sum of the product's
+// `splits` partial sums (+ bias), then xn[m] = norm(residual[m]) for the next product, one pass over the row with its
+// values in registers (one block per row, up to PER values a thread).  splits = 0: the product has already been
+// added to the stream, only the norm is left.  With `mu`, the token shift of a step in which every request brings ONE
+// token: row m is request m, the previous token's h comes from the request's slot and the row's h is left there.
+constexpr int LNT_PER = 16;
+
+template <typename TO, int PER>
+__global__ void __launch_bounds__(1024)
+reduce_residual_layernorm_kernel(const float *partial, int splits, int M, int N, const void *bias, int bias_dt, float *residual,
+                                 const float *w, float eps, int center, const float *mu, float *state, size_t slot_stride,
+                                 const int32_t *seq_slots, int n_slots, TO *xn, int *err)
+{
+    pdl_entry();
+    __shared__ float red[32];
+    const int m = blockIdx.x;
+    float vals[PER];
+    pdl_sync_small();
+    const size_t MN = (size_t)M * N;
+    float *res = residual + (size_t)m * N;
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; j++) vals[j] = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += 4) {              // four splits' reads in flight for every value: their latency is what this costs
+        float q[4][PER];
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+#pragma unroll
+            for (int j = 0; j < PER; j++) {
+                const int i = threadIdx.x + j * blockDim.x;
+                q[k][j] = (s0 + k < splits && i < N) ? partial[(size_t)(s0 + k) * MN + (size_t)m * N + i] : 0.f;
+            }
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+#pragma unroll
+            for (int j = 0; j < PER; j++) vals[j] += q[k][j];
+    }
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        float v = vals[j];
+        if (i < N) {
+            if (bias) v += load_any(bias, bias_dt, i);
+            v += res[i];
+            if (splits > 0 || bias) res[i] = v;
+        }
+        vals[j] = v;
+        sum += v;
+    }
+    if (!xn) return;
+    const float mean = center ? ln_block_sum(sum, red) / (float)N : 0.f;
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        const float d = i < N ? vals[j] - mean : 0.f;
+        ss = fmaf(d, d, ss);
+    }
+    const float r = 1.0f / sqrtf(ln_block_sum(ss, red) / (float)N + eps);
+    float *st = nullptr;
+    if (mu) {
+        const int slot = seq_slots[m];
+        if (slot < 0 || slot >= n_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
+        st = state + (size_t)slot * slot_stride;
+    }
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i >= N) continue;
+        float h = (vals[j] - mean) * r * w[i];
+        if (mu) {
+            const float before = st[i];
+            st[i] = h;
+            h = fmaf(before - h, mu[i], h);
+        }
+        xn[(size_t)m * N + i] = from_f32<TO>(h);
+    }
+}
+
 }  // namespace hfb
 
 using namespace hfb;
@@ -174,4 +254,26 @@ extern "C" int hfb_gate_mul(const void *a, int dt, const float *g, int splits, i
         g_launch_err = launch_pdl(gate_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, (const __nv_bfloat16 *)a, g,
                                   splits, g_stride, g_col0, bias, gate, (__nv_bfloat16 *)out, T, C);
     return check_pdl_launch(g_launch_err, "gate_mul");
+}
+
+extern "C" int hfb_reduce_residual_layernorm(const float *partial, int splits, int M, int N, const void *bias, int bias_dt,
+                                             float *residual, const float *w, float eps, int center, const float *mu, float *state,
+                                             int64_t slot_stride, const int32_t *seq_slots, int n_slots, void *xn, int xn_dt,
+                                             hfb_stream s)
+{
+    if (M <= 0) return HFB_OK;
+    if (splits < 0 || (splits > 0 && !partial) || N <= 0 || !residual || (bias && !valid_dt(bias_dt)) || (xn && (!w || !valid_dt(xn_dt))) ||
+        (mu && (!xn || !state || !seq_slots || slot_stride < N)))
+        return fail(HFB_EINVAL, "reduce_residual_layernorm: bad arguments (N=%d splits=%d)", N, splits);
+    if (N > LNT_PER * 1024) return fail(HFB_ENOTSUP, "reduce_residual_layernorm: rows of %d values exceed %d", N, LNT_PER * 1024);
+    int threads = ((N + 3) / 4 + 31) / 32 * 32;           // four values a thread where the row allows
+    if (threads > 1024) threads = 1024;
+#define HFB_LNT(TY, PER) \
+    g_launch_err = launch_pdl(reduce_residual_layernorm_kernel<TY, PER>, dim3(M), dim3(threads), 0, (cudaStream_t)s, partial, splits, M, N, bias, \
+                              bias_dt, residual, w, eps, center, mu, state, (size_t)slot_stride, seq_slots, n_slots, (TY *)xn, error_word())
+    const bool few = N <= 4 * threads;                     // rows of up to 4,096 values: four a thread, all in registers
+    if (xn_dt == HFB_F32 || !xn) { if (few) HFB_LNT(float, 4); else HFB_LNT(float, LNT_PER); }
+    else { if (few) HFB_LNT(__nv_bfloat16, 4); else HFB_LNT(__nv_bfloat16, LNT_PER); }
+#undef HFB_LNT
+    return check_pdl_launch(g_launch_err, "reduce_residual_layernorm");
 }

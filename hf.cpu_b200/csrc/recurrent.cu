@@ -301,21 +301,22 @@ static unsigned rec_blocks(size_t total)
 // planes [T, 3 W], and biases on the first two:
 //     z = sigmoid(a + bz);  u = b + bx;  cand = u >= 0 ? u + 1/2 : sigmoid(u);  S <- (1 - z) S + z cand;
 //     out = S * silu(g)
-// S [W] float32 per request lives in its state slot.  A block takes MG_CH channels of one request.  Its warps first
-// compute, for a chunk of MG_CT tokens, everything that does not depend on S (z, z * cand, silu(g): three exponentials
-// a token and channel) into shared memory, in parallel over tokens; then the first warp walks the chunk, one channel a
-// lane, two multiply-adds a token, while the other warps already work on the next chunk (two buffers).  The walk is
-// the same sequence of operations whatever the step's cutting, so a position's result does not depend on it.
-constexpr int MG_CH = 32, MG_CT = 32, MG_WARPS = 8;
+// S [W] float32 per request lives in its state slot.  A block takes MG_CH channels of one request.  Its fill warps
+// compute, for a chunk of MG_CT tokens, everything that does not depend on S (1 - z, z * cand, silu(g): three
+// exponentials a token and channel) into shared memory, in parallel over tokens, from operands they requested one chunk
+// earlier (MG_PER tokens a thread, all of a chunk's reads in flight together: their latency is what a chunk would
+// cost); meanwhile the first warp walks the chunk before, one channel a lane, a multiply-add a token.  The walk is the
+// same sequence of operations whatever the step's cutting, so a position's result does not depend on it.
+constexpr int MG_CH = 32, MG_FILL = 8, MG_PER = 8, MG_CT = MG_FILL * MG_PER;
 
 template <typename TO>
-__global__ void __launch_bounds__(MG_WARPS * 32)
+__global__ void __launch_bounds__((MG_FILL + 1) * 32)
 mingru_scan_kernel(const float *row, int splits, const void *bz, const void *bx, int b_dt, float *state, size_t slot_stride,
                    const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, TO *out, int T, int W, int *err)
 {
     pdl_entry();
     pdl_sync_small();
-    __shared__ float s_z[2][MG_CT][MG_CH], s_b[2][MG_CT][MG_CH], s_g[2][MG_CT][MG_CH];
+    __shared__ float s_a[2][MG_CT][MG_CH], s_b[2][MG_CT][MG_CH], s_g[2][MG_CT][MG_CH];
     const int seq = blockIdx.y, c0 = blockIdx.x * MG_CH;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int c = c0 + lane;
@@ -324,43 +325,61 @@ mingru_scan_kernel(const float *row, int splits, const void *bz, const void *bx,
     if (slot < 0 || slot >= n_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
     const int t0 = cu_tokens[seq], n = cu_tokens[seq + 1] - t0;
     const size_t C3 = 3 * (size_t)W, plane = (size_t)T * C3;
-    const float vbz = (live && bz) ? load_any(bz, b_dt, c) : 0.f, vbx = (live && bx) ? load_any(bx, b_dt, c) : 0.f;
-    float S = (warp == 0 && live) ? state[(size_t)slot * slot_stride + c] : 0.f;
     const int chunks = (n + MG_CT - 1) / MG_CT;
+    const int fw = warp - 1;                           // which of the fill warps (the first warp walks)
+    const float vbz = (live && bz) ? load_any(bz, b_dt, c) : 0.f, vbx = (live && bx) ? load_any(bx, b_dt, c) : 0.f;
+    float ra[MG_PER], rb[MG_PER], rg[MG_PER];          // a chunk's operands on their way: tokens fw, fw + MG_FILL, ...
 
-    auto fill = [&](int k, int first, int stride) {
-        // tokens k * MG_CT + first, + stride, ... of the request's share of the step
-        const int buf = k & 1;
-        for (int j = first; j < MG_CT; j += stride) {
-            const int i = k * MG_CT + j;
-            if (i >= n || !live) continue;
-            const float *p = row + (size_t)(t0 + i) * C3 + c;
-            float a = 0.f, b = 0.f, g = 0.f;
-            for (int s = 0; s < splits; s++) {
-                a += p[(size_t)s * plane]; b += p[(size_t)s * plane + W]; g += p[(size_t)s * plane + 2 * (size_t)W];
+    auto request = [&](int k) {
+#pragma unroll
+        for (int u = 0; u < MG_PER; u++) ra[u] = rb[u] = rg[u] = 0.f;
+        for (int s = 0; s < splits; s++) {
+#pragma unroll
+            for (int u = 0; u < MG_PER; u++) {
+                const int i = k * MG_CT + fw + u * MG_FILL;
+                if (i < n && live) {
+                    const float *p = row + (size_t)s * plane + (size_t)(t0 + i) * C3 + c;
+                    ra[u] += p[0]; rb[u] += p[W]; rg[u] += p[2 * (size_t)W];
+                }
             }
-            const float z = sigmoid_f(a + vbz), u = b + vbx;
-            const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
-            s_z[buf][j][lane] = z;
+        }
+    };
+    auto finish = [&](int k) {
+        const int buf = k & 1;
+#pragma unroll
+        for (int u = 0; u < MG_PER; u++) {
+            const int j = fw + u * MG_FILL;
+            const float z = sigmoid_f(ra[u] + vbz), v = rb[u] + vbx, g = rg[u];
+            const float cand = v >= 0.f ? v + 0.5f : sigmoid_f(v);
+            s_a[buf][j][lane] = 1.0f - z;
             s_b[buf][j][lane] = z * cand;
             s_g[buf][j][lane] = g * sigmoid_f(g);
         }
     };
 
-    fill(0, warp, MG_WARPS);
+    float S = 0.f;
+    if (warp == 0) {
+        if (live) S = state[(size_t)slot * slot_stride + c];
+    } else {
+        request(0);
+        finish(0);
+        if (chunks > 1) request(1);
+    }
     __syncthreads();
     for (int k = 0; k < chunks; k++) {
         if (warp == 0) {
             const int buf = k & 1, m = min(MG_CT, n - k * MG_CT);
             if (live) {
                 TO *o = out + (size_t)(t0 + k * MG_CT) * W + c;
+#pragma unroll 4
                 for (int j = 0; j < m; j++) {
-                    S = fmaf(1.0f - s_z[buf][j][lane], S, s_b[buf][j][lane]);
+                    S = fmaf(s_a[buf][j][lane], S, s_b[buf][j][lane]);
                     o[(size_t)j * W] = from_f32<TO>(S * s_g[buf][j][lane]);
                 }
             }
         } else if (k + 1 < chunks) {
-            fill(k + 1, warp - 1, MG_WARPS - 1);
+            finish(k + 1);
+            if (k + 2 < chunks) request(k + 2);
         }
         __syncthreads();
     }
@@ -462,11 +481,12 @@ extern "C" int hfb_mingru_scan(const float *row, int splits, const void *bz, con
         return fail(HFB_EINVAL, "mingru_scan: bad arguments (W=%d)", W);
     if (S > 65535) return fail(HFB_ENOTSUP, "mingru_scan: %d requests exceed the grid limit", S);
     const dim3 grid((W + MG_CH - 1) / MG_CH, S);
+    const dim3 block((MG_FILL + 1) * 32);
     if (out_dt == HFB_F32)
-        g_launch_err = launch_pdl(mingru_scan_kernel<float>, grid, dim3(MG_WARPS * 32), 0, (cudaStream_t)s, row, splits, bz, bx, b_dt, state,
+        g_launch_err = launch_pdl(mingru_scan_kernel<float>, grid, block, 0, (cudaStream_t)s, row, splits, bz, bx, b_dt, state,
                                   (size_t)slot_stride, cu_tokens, seq_slots, n_slots, (float *)out, T, W, error_word());
     else
-        g_launch_err = launch_pdl(mingru_scan_kernel<__nv_bfloat16>, grid, dim3(MG_WARPS * 32), 0, (cudaStream_t)s, row, splits, bz, bx, b_dt,
+        g_launch_err = launch_pdl(mingru_scan_kernel<__nv_bfloat16>, grid, block, 0, (cudaStream_t)s, row, splits, bz, bx, b_dt,
                                   state, (size_t)slot_stride, cu_tokens, seq_slots, n_slots, (__nv_bfloat16 *)out, T, W, error_word());
     return check_pdl_launch(g_launch_err, "mingru_scan");
 }

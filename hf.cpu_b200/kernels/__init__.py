@@ -254,12 +254,24 @@ def linear_swiglu(a: torch.Tensor, w: torch.Tensor, gu_buf: torch.Tensor, out: t
     backend().linear_swiglu(a, w, gu_buf, out)
 
 
-def linear_residual_norm(a, w, bias, residual, norm_w, eps, xn_out) -> None:
-    """residual += a @ w.T (+ bias); then, if ``xn_out`` is given, xn_out = rmsnorm(residual) * norm_w."""
+def linear_residual_norm(a, w, bias, residual, norm_w, eps, xn_out, center: bool = False, shift=None) -> None:
+    """residual += a @ w.T (+ bias); then, if ``xn_out`` is given, xn_out = rmsnorm(residual) * norm_w.  ``center``: the
+    norm takes the mean off first (layer norm; ``norm_w`` float32).  ``shift`` = (mu, state, seq_slots), for a step in which
+    every request brings one token: xn_out = h + (previous h - h) * mu with h the norm's output, the previous h from the
+    request's row of ``state`` (float32 [slots, N]), which then receives h (``norm_w`` and ``mu`` float32)."""
     _need(a.shape[1] == w.shape[1] and residual.shape == (a.shape[0], w.shape[0]) and residual.dtype == torch.float32,
           "linear_residual_norm: shape mismatch")
     _need(xn_out is None or (xn_out.shape == residual.shape and norm_w.shape == (w.shape[0],)),
           "linear_residual_norm: norm shape mismatch")
+    if center or shift is not None:
+        _need(xn_out is not None and norm_w.dtype == torch.float32, "linear_residual_norm: this norm takes a float32 weight")
+        if shift is not None:
+            mu, state, seq_slots = shift
+            _need(mu.shape == (w.shape[0],) and mu.dtype == torch.float32 and state.dtype == torch.float32 and state.dim() == 2
+                  and state.shape[1] == w.shape[0] and seq_slots.shape[0] == a.shape[0],
+                  "linear_residual_norm: the shift takes (float32 [N], float32 [slots, N], a slot per row)")
+        backend().linear_residual_norm(a, w, bias, residual, norm_w, float(eps), xn_out, center=bool(center), shift=shift)
+        return
     backend().linear_residual_norm(a, w, bias, residual, norm_w, float(eps), xn_out)
 
 

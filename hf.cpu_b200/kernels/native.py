@@ -309,11 +309,26 @@ class NativeBackend:
         self.linear(a, w, None, gu_buf, False)
         self.swiglu(gu_buf, out, True)
 
-    def linear_residual_norm(self, a, w, bias, residual, norm_w, eps, xn_out):
+    def linear_residual_norm(self, a, w, bias, residual, norm_w, eps, xn_out, center=False, shift=None):
         self._on_gpu(a, w, bias, residual, norm_w, xn_out)
         M, K = a.shape
         N = w.shape[0]
         part = self._partials(a, w) if self._tc_ok(a, w) else None
+        if center or shift is not None:
+            # layer norm and the token shift of single-token steps: a tail of their own; where the product is not split
+            # it is added to the stream first and the tail only norms
+            ws, splits = part if part is not None else (None, 0)
+            if part is None:
+                self.linear(a, w, bias, residual, True)
+                bias = None
+            mu, state, seq_slots = shift if shift is not None else (None, None, None)
+            self._on_gpu(mu, state, seq_slots)
+            self._check(self.lib.hfb_reduce_residual_layernorm(
+                _p(ws), c_int(splits), c_int(M), c_int(N), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(residual),
+                _p(norm_w), c_float(eps), c_int(1 if center else 0), _p(mu), _p(state),
+                c_int64(state.stride(0) if state is not None else 0), _p(seq_slots), c_int(state.shape[0] if state is not None else 0),
+                _p(xn_out), c_int(_dt(xn_out)), self._stream()), "reduce_residual_layernorm")
+            return
         if part is None:
             self.linear(a, w, bias, residual, True)
             if xn_out is not None:

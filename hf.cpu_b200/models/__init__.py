@@ -136,8 +136,16 @@ class Model:
             extra = layer.post_norms()
             if i + 1 < len(schedule):
                 next_norm = self.layers[schedule[i + 1].layer].norm1
+                following = self.layers[schedule[i + 1].layer].block
                 if getattr(layer.block, "wants_next_block", False):
-                    extra["next_block"] = self.layers[schedule[i + 1].layer].block
+                    extra["next_block"] = following
+                if following.state_spec() is not None:
+                    # a block with state of its own (a token shift) makes its mixer's input itself, unless the block in
+                    # front knows how to
+                    if getattr(layer.block, "fuses_next_shift", False):
+                        extra["next_block_state"] = ctx.entry_state(block_state_key(i + 1))
+                    else:
+                        next_norm = None
             else:
                 next_norm = self.final_norm if getattr(ctx, "logits_for_all", False) else None
             if layer.block.state_spec() is not None:

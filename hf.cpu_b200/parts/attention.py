@@ -75,7 +75,7 @@ class OutputProduct:
             return False
         att = self._attend(ctx, xn, cache, write_cache)
         with kernels.phase("wo"):
-            kernels.linear_residual_norm(att, self.w_o, self.b_o, residual, args[0], args[1], out)
+            kernels.linear_residual_norm(att, self.w_o, self.b_o, residual, args[0], args[1], out, **(args[2] if len(args) > 2 else {}))
         return True
 
 

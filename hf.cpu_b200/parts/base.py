@@ -107,7 +107,8 @@ class Part:
 
 class Norm(Part):
     def fused_args(self):
-        """(weight, eps) when this norm is an RMSNorm that a product's tail may apply itself, else None."""
+        """(weight, eps) when this norm is an RMSNorm that a product's tail may apply itself, (weight, eps, options of
+        ``kernels.linear_residual_norm``) for other norms that tail knows, else None."""
         return None
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:

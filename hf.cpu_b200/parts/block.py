@@ -11,6 +11,7 @@ from .. import kernels
 from ..config.base import UnsupportedError
 from ..weights.loader import TensorSpec
 from .base import Block, StateSpec, register_part
+from .norm import ShiftedNorm
 
 
 class PreNormResidual(Block):
@@ -20,6 +21,8 @@ class PreNormResidual(Block):
     schedule entry, so that a step may bring only the next token of a request.  The feed-forward reads ``norm2(x)`` as
     it is."""
     graph_safe = True
+    wants_next_block = True          # the model hands the following block over, for its shift
+    fuses_next_shift = True          # ... and may be given the following block's first norm although that block shifts
 
     def __init__(self, token_shift=None, hidden_size: int = 0, **_):
         self.shift_tensor, self.E = token_shift, int(hidden_size)
@@ -37,21 +40,28 @@ class PreNormResidual(Block):
     def state_spec(self):
         return StateSpec((self.E,)) if self.shift_tensor else None
 
-    def forward(self, ctx, x, norm1, mixer, norm2, ffn, cache, state, write_cache, xn_ready=None, next_norm=None, block_state=None):
-        if self.shift_tensor:
+    def forward(self, ctx, x, norm1, mixer, norm2, ffn, cache, state, write_cache, xn_ready=None, next_norm=None, block_state=None,
+                next_block=None, next_block_state=None):
+        if xn_ready is not None:
+            xn = xn_ready                 # (from a block that knew of this block's shift, if it has one)
+        elif self.shift_tensor:
             args = getattr(norm1, "shift_args", None)
             if args is None or block_state is None:
                 raise UnsupportedError("the token shift needs a norm that offers it and the block's per-request state")
             xn = ctx.buf("block_xn", x.shape, ctx.run_dtype)
             with kernels.phase("glue"):
                 kernels.norm_shift(x, *args(), self.mu, block_state, ctx, xn)
-        elif xn_ready is None:
+        else:
             xn = ctx.buf("block_xn", x.shape, ctx.run_dtype)
             norm1.forward(x, xn)
-        else:
-            xn = xn_ready
-        if self.shift_tensor:
-            next_norm = None              # the following block shifts its own normed input: nothing to hand over
+        if next_norm is not None and getattr(next_block, "shift_tensor", None):
+            # the following block shifts its normed input.  In a step of single tokens the previous row of every request
+            # is in its slot, and the tail of this block's last product can do norm, shift and the slot's update; in any
+            # other step that block does it itself, in the kernel that sees a request's rows side by side
+            if ctx.max_q_len == 1 and next_block_state is not None and hasattr(next_norm, "shift_args"):
+                next_norm = ShiftedNorm(next_norm, next_block.mu, next_block_state, ctx)
+            else:
+                next_norm = None
         if ffn is None:
             # a layer that is a mixer only: the norm behind its product is the next block's first
             fused = getattr(mixer, "forward_then_norm", None) if next_norm is not None else None

@@ -68,7 +68,7 @@ class SwiGlu(FeedForward):
             return False
         h = self._hidden(ctx, xn)
         with kernels.phase("down"):
-            kernels.linear_residual_norm(h, self.w_down, None, residual, args[0], args[1], out)
+            kernels.linear_residual_norm(h, self.w_down, None, residual, args[0], args[1], out, **(args[2] if len(args) > 2 else {}))
         return True
 
 
@@ -124,7 +124,7 @@ class Mlp(FeedForward):
             return False
         h = self._hidden(ctx, xn)
         with kernels.phase("down"):
-            kernels.linear_residual_norm(h, self.w_down, None, residual, args[0], args[1], out)
+            kernels.linear_residual_norm(h, self.w_down, None, residual, args[0], args[1], out, **(args[2] if len(args) > 2 else {}))
         return True
 
 

@@ -65,12 +65,34 @@ class LayerNorm(Norm):
             return
         self.weight = tensors[self.tensor].to(torch.float32).contiguous()
 
+    def fused_args(self):
+        return self.weight, self.eps, {"center": True}
+
     def shift_args(self):
         return self.weight, self.eps, True
 
     def forward(self, x, out, rows=None):
         with kernels.phase("glue"):
             kernels.layernorm(x, self.weight, self.eps, out, rows)
+        return out
+
+
+class ShiftedNorm(Norm):
+    """A norm with the token shift of the block behind it, as one object that a sublayer's last product can be handed: in
+    a step in which every request brings one token, that product's tail norms the new stream, shifts it by the
+    request's previous row and leaves the new row in its place.  Made per step by the block in front; not registered."""
+
+    def __init__(self, norm, mu, state, ctx):
+        self.norm, self.mu, self.state, self.ctx = norm, mu, state, ctx
+
+    def fused_args(self):
+        w, eps, center = self.norm.shift_args()
+        return w, eps, {"center": center, "shift": (self.mu, self.state, self.ctx.seq_slots)}
+
+    def forward(self, x, out, rows=None):
+        w, eps, center = self.norm.shift_args()
+        with kernels.phase("glue"):
+            kernels.norm_shift(x, w, eps, center, self.mu, self.state, self.ctx, out)
         return out
 
 

@@ -57,7 +57,7 @@ class _Recurrent(OutputProduct, Mixer):
             return False
         att = self._attend(ctx, xn, cache, write_cache, state)
         with kernels.phase("wo"):
-            kernels.linear_residual_norm(att, self.w_o, None, residual, args[0], args[1], out)
+            kernels.linear_residual_norm(att, self.w_o, None, residual, args[0], args[1], out, **(args[2] if len(args) > 2 else {}))
         return True
 
     def _low_rank_sums(self, ctx, xn, w1, w2, tag):

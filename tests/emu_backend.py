@@ -111,10 +111,21 @@ class EmuBackend:
         self.linear(a, w, None, gu_buf, False)
         self.swiglu(gu_buf, out, True)
 
-    def linear_residual_norm(self, a, w, bias, residual, norm_w, eps, xn_out):
+    def linear_residual_norm(self, a, w, bias, residual, norm_w, eps, xn_out, center=False, shift=None):
         self.linear(a, w, bias, residual, True)
-        if xn_out is not None:
+        if xn_out is None:
+            return
+        if not center and shift is None:
             self.rmsnorm(residual, norm_w, eps, xn_out, None)
+            return
+        h = self._norm_rows(residual, norm_w, eps, center)
+        if shift is not None:                   # a step of single tokens: row m is request m
+            mu, state, seq_slots = shift
+            slots = seq_slots.long()
+            before = state[slots].clone()
+            state[slots] = h
+            h = h + (before - h) * mu
+        xn_out.copy_(h.to(xn_out.dtype))
 
     def linear_rope_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d):
         self.linear(a, w, bias, qkv_buf, False)

@@ -146,6 +146,41 @@ def test_mingru_whole_against_cut(dtype, W, E):
     K().check_device_errors()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", [(1, 72, 100), (5, 256, 512), (8, 2048, 1024), (130, 256, 320), (3, 44, 24), (2, 5000, 64)])
+def test_product_tail_with_layer_norm_and_shift(dtype, shape):
+    """The last product of a sublayer with what follows it in one call: the sum with the stream, the layer norm of the new
+    stream, and, for steps of single tokens, the shift by each request's previous row with the slot's update; two such
+    steps in a row over slots in scrambled order."""
+    M, N, Kd = shape
+    dt, r, eps = DT[dtype], rng(sum(shape)), 1e-5
+    a, w, bias = dev(r.standard_normal((M, Kd)), dt), dev(0.2 * r.standard_normal((N, Kd)), dt), dev(r.standard_normal(N), dt)
+    nw, mu = dev(r.uniform(0.5, 1.5, N)), dev(r.uniform(-0.3, 1.2, N))
+    res = dev(r.standard_normal((M, N)) + 3.0)
+    want_res = f64(res) + f64(a) @ f64(w).T + f64(bias)
+    want_h = plain.layer_norm(want_res, f64(nw), eps)
+    out_res, xn = res.clone(), torch.empty(M, N, dtype=dt, device=DEV)
+    K().linear_residual_norm(a, w, bias, out_res, nw, eps, xn, center=True)
+    tol = 2e-5 if dtype == "float32" else 2e-2
+    assert rel(out_res, want_res) < tol and rel(xn, plain.layer_norm(f64(out_res), f64(nw), eps)) < (1e-5 if dtype == "float32" else KTOL[dtype])
+    slots = r.permutation(M + 2)[:M]
+    state = dev(r.standard_normal((M + 2, N)))
+    before = f64(state)
+    seq_slots = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    out_res = res.clone()
+    K().linear_residual_norm(a, w, bias, out_res, nw, eps, xn, center=True, shift=(mu, state, seq_slots))
+    h = plain.layer_norm(f64(out_res), f64(nw), eps)
+    assert rel(xn, h + (before[slots] - h) * f64(mu)) < (1e-5 if dtype == "float32" else KTOL[dtype])
+    assert rel(state[seq_slots.long()], h) < 1e-5 and float(np.abs(h - want_h).max() / np.abs(want_h).max()) < tol
+    untouched = [s for s in range(M + 2) if s not in set(slots.tolist())]
+    assert torch.equal(state[untouched].cpu(), torch.as_tensor(before[untouched], dtype=torch.float32))
+    res2 = out_res.clone()
+    K().linear_residual_norm(a, w, None, res2, nw, eps, xn, center=True, shift=(mu, state, seq_slots))
+    h2 = plain.layer_norm(f64(res2), f64(nw), eps)
+    assert rel(xn, h2 + (h - h2) * f64(mu)) < (2e-5 if dtype == "float32" else KTOL[dtype])
+    K().check_device_errors()
+
+
 def plain_scores_attend(q, k, v, positions, lo_of, scale, temp, cap, H, G):
     """q [n, H, d] at ``positions`` over keys k [m, G, d], values v [m, G, dv]; query i sees keys lo_of(pos) .. pos."""
     out = np.zeros((q.shape[0], H, v.shape[-1]))
