@@ -19,8 +19,10 @@ namespace hfb {
 int *error_word();
 
 constexpr int LN_THREADS = 256;
+constexpr int LNT_PER = 16;         // values a thread holds of a row of more than 8,192 (the register kernels)
 
-// Sum over the block, the same value in every thread; `red` holds one float per warp.
+// Sum over the block, the same value in every thread; `red` holds one float per warp.  The warps' sums meet in one more
+// warp-wide sum that every warp makes for itself: one fixed order, whatever the block's size.
 __device__ __forceinline__ float ln_block_sum(float v, float *red)
 {
     v = warp_sum(v);
@@ -28,9 +30,7 @@ __device__ __forceinline__ float ln_block_sum(float v, float *red)
     __syncthreads();                                   // the last sum's readers are done with red
     if (lane == 0) red[warp] = v;
     __syncthreads();
-    float t = 0.f;
-    for (int i = 0; i < (int)(blockDim.x >> 5); i++) t += red[i];
-    return t;
+    return warp_sum(lane < (int)(blockDim.x >> 5) ? red[lane] : 0.f);
 }
 
 // row[i] = norm(x)[i] for the thread's own i (i = threadIdx.x, + blockDim.x, ...): nobody reads another thread's entries.
@@ -61,41 +61,85 @@ layernorm_kernel(const float *x, const float *w, float eps, int center, const in
     for (int i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)r * E + i] = from_f32<TO>(row[i]);
 }
 
-// out[t] = h_t + (h_(t-1) - h_t) * mu with h = norm(x); one block per token.  state [slots][slot_stride] float32.
-template <typename TO>
-__global__ void __launch_bounds__(LN_THREADS)
+// Two sums over the block at once.
+__device__ __forceinline__ void ln_block_sum2(float &a, float &b, float *red)
+{
+    a = warp_sum(a);
+    b = warp_sum(b);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) { red[warp] = a; red[32 + warp] = b; }
+    __syncthreads();
+    a = warp_sum(lane < nw ? red[lane] : 0.f);
+    b = warp_sum(lane < nw ? red[32 + lane] : 0.f);
+}
+
+// out[t] = h_t + (h_(t-1) - h_t) * mu with h = norm(x); one block per token, a row's values in registers (PER a thread).
+// A block norms two rows side by side, its own and one other: the previous token's where that is in this step (its norm
+// is made again here rather than passed between blocks), or, in the block of a request's first token of the step, the
+// request's last token's, which goes to the slot.  state [slots][slot_stride] float32.
+template <typename TO, int PER>
+__global__ void __launch_bounds__(1024)
 layernorm_shift_kernel(const float *x, const float *w, const float *mu, float eps, int center, float *state, size_t slot_stride,
                        const int32_t *token_seq, const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, TO *out, int T,
                        int E, int *err)
 {
     pdl_entry();
     pdl_sync_small();
-    extern __shared__ float ln_smem[];
-    float *mine = ln_smem, *other = ln_smem + E, *red = ln_smem + 2 * E;
+    __shared__ float red[64];
     const int t = blockIdx.x;
     const int seq = token_seq[t];
     const int t0 = cu_tokens[seq], t_last = cu_tokens[seq + 1] - 1;
-    ln_row(x + (size_t)t * E, w, eps, center, E, mine, red);
-    if (t > t0) {
-        // the previous token's row is in this step: its norm is made again here rather than passed between blocks
-        ln_row(x + (size_t)(t - 1) * E, w, eps, center, E, other, red);
-        for (int i = threadIdx.x; i < E; i += blockDim.x) {
-            const float h = mine[i];
-            out[(size_t)t * E + i] = from_f32<TO>(fmaf(other[i] - h, mu[i], h));
+    const bool first = t == t0;
+    const int t_other = first ? t_last : t - 1;
+    const bool two = t_other != t;
+    float *st = nullptr;
+    if (first) {
+        const int slot = seq_slots[seq];
+        if (slot < 0 || slot >= n_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
+        st = state + (size_t)slot * slot_stride;
+    }
+    const float *xa = x + (size_t)t * E, *xb = x + (size_t)t_other * E;
+    float va[PER], vb[PER];
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        va[j] = i < E ? xa[i] : 0.f;
+        vb[j] = (two && i < E) ? xb[i] : 0.f;
+        sa += va[j];
+        sb += vb[j];
+    }
+    float mean_a = 0.f, mean_b = 0.f;
+    if (center) {
+        ln_block_sum2(sa, sb, red);
+        mean_a = sa / (float)E;
+        mean_b = sb / (float)E;
+    }
+    float qa = 0.f, qb = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        const float da = i < E ? va[j] - mean_a : 0.f, db = i < E ? vb[j] - mean_b : 0.f;
+        qa = fmaf(da, da, qa);
+        qb = fmaf(db, db, qb);
+    }
+    ln_block_sum2(qa, qb, red);
+    const float ra = 1.0f / sqrtf(qa / (float)E + eps), rb = 1.0f / sqrtf(qb / (float)E + eps);
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i >= E) continue;
+        const float wi = w[i];
+        const float h = (va[j] - mean_a) * ra * wi;
+        const float other = two ? (vb[j] - mean_b) * rb * wi : h;
+        float before;
+        if (first) {
+            before = st[i];
+            st[i] = other;                           // the request's last row of the step (this one, if it is the only one)
+        } else {
+            before = other;
         }
-        return;
-    }
-    const int slot = seq_slots[seq];
-    if (slot < 0 || slot >= n_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
-    float *st = state + (size_t)slot * slot_stride;
-    const float *leave = mine;
-    if (t_last > t) {
-        ln_row(x + (size_t)t_last * E, w, eps, center, E, other, red);
-        leave = other;
-    }
-    for (int i = threadIdx.x; i < E; i += blockDim.x) {
-        const float h = mine[i], before = st[i];
-        st[i] = leave[i];
         out[(size_t)t * E + i] = from_f32<TO>(fmaf(before - h, mu[i], h));
     }
 }
@@ -126,8 +170,6 @@ __global__ void gate_mul_kernel(const TA *a, const float *g, int splits, int g_s
 // values in registers (one block per row, up to PER values a thread).  splits = 0: the product has already been
 // added to the stream, only the norm is left.  With `mu`, the token shift of a step in which every request brings ONE
 // token: row m is request m, the previous token's h comes from the request's slot and the row's h is left there.
-constexpr int LNT_PER = 16;
-
 template <typename TO, int PER>
 __global__ void __launch_bounds__(1024)
 reduce_residual_layernorm_kernel(const float *partial, int splits, int M, int N, const void *bias, int bias_dt, float *residual,
@@ -144,17 +186,18 @@ reduce_residual_layernorm_kernel(const float *partial, int splits, int M, int N,
     float sum = 0.f;
 #pragma unroll
     for (int j = 0; j < PER; j++) vals[j] = 0.f;
-    for (int s0 = 0; s0 < splits; s0 += 4) {              // four splits' reads in flight for every value: their latency is what this costs
-        float q[4][PER];
+    constexpr int FLY = PER <= 8 ? 32 / PER : 1;          // splits whose reads are in flight together: their latency is what this costs
+    for (int s0 = 0; s0 < splits; s0 += FLY) {
+        float q[FLY][PER];
 #pragma unroll
-        for (int k = 0; k < 4; k++)
+        for (int k = 0; k < FLY; k++)
 #pragma unroll
             for (int j = 0; j < PER; j++) {
                 const int i = threadIdx.x + j * blockDim.x;
                 q[k][j] = (s0 + k < splits && i < N) ? partial[(size_t)(s0 + k) * MN + (size_t)m * N + i] : 0.f;
             }
 #pragma unroll
-        for (int k = 0; k < 4; k++)
+        for (int k = 0; k < FLY; k++)
 #pragma unroll
             for (int j = 0; j < PER; j++) vals[j] += q[k][j];
     }
@@ -200,6 +243,129 @@ reduce_residual_layernorm_kernel(const float *partial, int splits, int M, int N,
     }
 }
 
+
+// The same tail with 16-byte accesses, for rows whose length is a multiple of four: PV float4 a thread.  Everything the
+// row needs is requested before anything is used (the request's slot first, then the partial sums, the stream's row,
+// the weights, the shift and the slot's row), so the pass costs about one round trip to memory and two block sums.
+__device__ __forceinline__ float4 f4_add(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+
+template <typename TO> __device__ __forceinline__ void store4(TO *p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float *p, float4 v) { *(float4 *)p = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16 *p, float4 v)
+{
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *(uint32_t *)&lo;
+    u.y = *(uint32_t *)&hi;
+    *(uint2 *)p = u;
+}
+
+template <typename TO, int PV>
+__global__ void __launch_bounds__(1024)
+reduce_residual_layernorm_vec_kernel(const float *partial, int splits, int M, int N, const void *bias, int bias_dt, float *residual,
+                                     const float *w, float eps, int center, const float *mu, float *state, size_t slot_stride,
+                                     const int32_t *seq_slots, int n_slots, TO *xn, int *err)
+{
+    pdl_entry();
+    __shared__ float red[32];
+    const int m = blockIdx.x, N4 = N >> 2;
+    pdl_sync_small();
+    int slot = 0;
+    if (mu) slot = seq_slots[m];
+    const size_t MN4 = ((size_t)M * N) >> 2;
+    const float4 *part = (const float4 *)partial + (size_t)m * N4;
+    float4 *res = (float4 *)(residual + (size_t)m * N);
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 vals[PV], wv[PV], muv[PV], bef[PV];
+    constexpr int FLY = PV == 1 ? 8 : 4 / PV;            // splits whose reads are in flight together (registers decide)
+    float4 acc[PV];
+#pragma unroll
+    for (int j = 0; j < PV; j++) acc[j] = zero;
+    for (int s0 = 0; s0 < splits; s0 += FLY) {
+        float4 q[FLY][PV];
+#pragma unroll
+        for (int k = 0; k < FLY; k++)
+#pragma unroll
+            for (int j = 0; j < PV; j++) {
+                const int i = threadIdx.x + j * blockDim.x;
+                q[k][j] = (s0 + k < splits && i < N4) ? part[(size_t)(s0 + k) * MN4 + i] : zero;
+            }
+        if (s0 == 0) {
+            // the row's other operands go out behind the first partial sums
+#pragma unroll
+            for (int j = 0; j < PV; j++) {
+                const int i = threadIdx.x + j * blockDim.x;
+                vals[j] = i < N4 ? res[i] : zero;
+                wv[j] = (xn && i < N4) ? ((const float4 *)w)[i] : zero;
+                muv[j] = (mu && i < N4) ? ((const float4 *)mu)[i] : zero;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < FLY; k++)
+#pragma unroll
+            for (int j = 0; j < PV; j++) acc[j] = f4_add(acc[j], q[k][j]);
+    }
+    if (splits == 0) {
+#pragma unroll
+        for (int j = 0; j < PV; j++) {
+            const int i = threadIdx.x + j * blockDim.x;
+            vals[j] = i < N4 ? res[i] : zero;
+            wv[j] = (xn && i < N4) ? ((const float4 *)w)[i] : zero;
+            muv[j] = (mu && i < N4) ? ((const float4 *)mu)[i] : zero;
+        }
+    }
+    float4 *st = nullptr;
+    if (mu) {
+        if (slot < 0 || slot >= n_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
+        st = (float4 *)(state + (size_t)slot * slot_stride);
+#pragma unroll
+        for (int j = 0; j < PV; j++) {
+            const int i = threadIdx.x + j * blockDim.x;
+            bef[j] = i < N4 ? st[i] : zero;
+        }
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < PV; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < N4) {
+            float4 v = acc[j];
+            if (bias) v = f4_add(v, make_float4(load_any(bias, bias_dt, 4 * i), load_any(bias, bias_dt, 4 * i + 1),
+                                                load_any(bias, bias_dt, 4 * i + 2), load_any(bias, bias_dt, 4 * i + 3)));
+            v = f4_add(v, vals[j]);
+            if (splits > 0 || bias) res[i] = v;
+            vals[j] = v;
+            sum += (v.x + v.y) + (v.z + v.w);
+        }
+    }
+    if (!xn) return;
+    const float mean = center ? ln_block_sum(sum, red) / (float)N : 0.f;
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PV; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < N4) {
+            const float4 v = vals[j];
+            const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+            ss += (a * a + b * b) + (c * c + d * d);
+        }
+    }
+    const float r = 1.0f / sqrtf(ln_block_sum(ss, red) / (float)N + eps);
+#pragma unroll
+    for (int j = 0; j < PV; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i >= N4) continue;
+        const float4 v = vals[j];
+        float4 h = make_float4((v.x - mean) * r * wv[j].x, (v.y - mean) * r * wv[j].y, (v.z - mean) * r * wv[j].z, (v.w - mean) * r * wv[j].w);
+        if (mu) {
+            st[i] = h;
+            h = make_float4(fmaf(bef[j].x - h.x, muv[j].x, h.x), fmaf(bef[j].y - h.y, muv[j].y, h.y),
+                            fmaf(bef[j].z - h.z, muv[j].z, h.z), fmaf(bef[j].w - h.w, muv[j].w, h.w));
+        }
+        store4<TO>(xn + (size_t)m * N + 4 * (size_t)i, h);
+    }
+}
+
 }  // namespace hfb
 
 using namespace hfb;
@@ -227,15 +393,16 @@ extern "C" int hfb_layernorm_shift(const float *x, const float *w, const float *
     if (T <= 0) return HFB_OK;
     if (!x || !w || !mu || !state || !token_seq || !cu_tokens || !seq_slots || !out || !valid_dt(out_dt) || E <= 0 || slot_stride < E)
         return fail(HFB_EINVAL, "layernorm_shift: bad arguments (E=%d)", E);
-    const size_t smem = (2 * (size_t)E + 32) * sizeof(float);
-    if (smem > 48 * 1024) return fail(HFB_ENOTSUP, "layernorm_shift: rows of %d values exceed %d", E, 24 * 256 - 16);
-    if (out_dt == HFB_F32)
-        g_launch_err = launch_pdl(layernorm_shift_kernel<float>, dim3(T), dim3(LN_THREADS), smem, (cudaStream_t)s, x, w, mu, eps, center, state,
-                                  (size_t)slot_stride, token_seq, cu_tokens, seq_slots, n_slots, (float *)out, T, E, error_word());
-    else
-        g_launch_err = launch_pdl(layernorm_shift_kernel<__nv_bfloat16>, dim3(T), dim3(LN_THREADS), smem, (cudaStream_t)s, x, w, mu, eps, center,
-                                  state, (size_t)slot_stride, token_seq, cu_tokens, seq_slots, n_slots, (__nv_bfloat16 *)out, T, E,
-                                  error_word());
+    if (E > LNT_PER * 1024) return fail(HFB_ENOTSUP, "layernorm_shift: rows of %d values exceed %d", E, LNT_PER * 1024);
+    int threads = ((E + 7) / 8 + 31) / 32 * 32;           // eight values a thread where the row allows
+    if (threads > 1024) threads = 1024;
+#define HFB_LNS(TY, PER) \
+    g_launch_err = launch_pdl(layernorm_shift_kernel<TY, PER>, dim3(T), dim3(threads), 0, (cudaStream_t)s, x, w, mu, eps, center, state, \
+                              (size_t)slot_stride, token_seq, cu_tokens, seq_slots, n_slots, (TY *)out, T, E, error_word())
+    const bool few = E <= 8 * threads;
+    if (out_dt == HFB_F32) { if (few) HFB_LNS(float, 8); else HFB_LNS(float, LNT_PER); }
+    else { if (few) HFB_LNS(__nv_bfloat16, 8); else HFB_LNS(__nv_bfloat16, LNT_PER); }
+#undef HFB_LNS
     return check_pdl_launch(g_launch_err, "layernorm_shift");
 }
 
@@ -266,14 +433,30 @@ extern "C" int hfb_reduce_residual_layernorm(const float *partial, int splits, i
         (mu && (!xn || !state || !seq_slots || slot_stride < N)))
         return fail(HFB_EINVAL, "reduce_residual_layernorm: bad arguments (N=%d splits=%d)", N, splits);
     if (N > LNT_PER * 1024) return fail(HFB_ENOTSUP, "reduce_residual_layernorm: rows of %d values exceed %d", N, LNT_PER * 1024);
-    int threads = ((N + 3) / 4 + 31) / 32 * 32;           // four values a thread where the row allows
+    auto aligned = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    // steps of few rows (their cost is latency) take the form with 16-byte accesses and everything requested up front;
+    // passes over thousands of rows run faster with eight values a thread and half as many threads
+    if (M <= 1024 && (N & 3) == 0 && N <= 16 * 1024 && aligned(partial) && aligned(residual) && aligned(w) && aligned(mu) && aligned(state) &&
+        aligned(xn) && (slot_stride & 3) == 0) {
+        // 16-byte accesses: one float4 a thread up to 4,096 values (a warp at least), then two, then four
+        const int N4 = N >> 2, pv = N4 <= 1024 ? 1 : (N4 <= 2048 ? 2 : 4);
+        int threads = ((N4 + pv - 1) / pv + 31) / 32 * 32;
+#define HFB_LNV(TY, PV) \
+    g_launch_err = launch_pdl(reduce_residual_layernorm_vec_kernel<TY, PV>, dim3(M), dim3(threads), 0, (cudaStream_t)s, partial, splits, M, N, \
+                              bias, bias_dt, residual, w, eps, center, mu, state, (size_t)slot_stride, seq_slots, n_slots, (TY *)xn, error_word())
+        if (xn_dt == HFB_F32 || !xn) { if (pv == 1) HFB_LNV(float, 1); else if (pv == 2) HFB_LNV(float, 2); else HFB_LNV(float, 4); }
+        else { if (pv == 1) HFB_LNV(__nv_bfloat16, 1); else if (pv == 2) HFB_LNV(__nv_bfloat16, 2); else HFB_LNV(__nv_bfloat16, 4); }
+#undef HFB_LNV
+        return check_pdl_launch(g_launch_err, "reduce_residual_layernorm");
+    }
+    int threads = ((N + 7) / 8 + 31) / 32 * 32;           // eight values a thread where the row allows
     if (threads > 1024) threads = 1024;
 #define HFB_LNT(TY, PER) \
     g_launch_err = launch_pdl(reduce_residual_layernorm_kernel<TY, PER>, dim3(M), dim3(threads), 0, (cudaStream_t)s, partial, splits, M, N, bias, \
                               bias_dt, residual, w, eps, center, mu, state, (size_t)slot_stride, seq_slots, n_slots, (TY *)xn, error_word())
-    const bool few = N <= 4 * threads;                     // rows of up to 4,096 values: four a thread, all in registers
-    if (xn_dt == HFB_F32 || !xn) { if (few) HFB_LNT(float, 4); else HFB_LNT(float, LNT_PER); }
-    else { if (few) HFB_LNT(__nv_bfloat16, 4); else HFB_LNT(__nv_bfloat16, LNT_PER); }
+    const bool few = N <= 8 * threads;                     // rows of up to 8,192 values: eight a thread, all in registers
+    if (xn_dt == HFB_F32 || !xn) { if (few) HFB_LNT(float, 8); else HFB_LNT(float, LNT_PER); }
+    else { if (few) HFB_LNT(__nv_bfloat16, 8); else HFB_LNT(__nv_bfloat16, LNT_PER); }
 #undef HFB_LNT
     return check_pdl_launch(g_launch_err, "reduce_residual_layernorm");
 }

@@ -24,6 +24,8 @@ constexpr int REC_MAX_D = 512;
 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+// the same from the special-function unit's exponential and reciprocal: relative error of a few 1e-7
+__device__ __forceinline__ float sigmoid_fast(float z) { return __fdividef(1.0f, 1.0f + __expf(-z)); }
 
 // a[t, h, i] = exp(-rate[h] * softplus(sign * (z[t, h, i] + bias[h, i]))), z the sum of `splits` planes [T, z_stride] read
 // from column z_col0 on.  sign = +1 with rate = exp(A_log): exp(-exp(A_log) softplus(z + dt_bias)); sign = -1 with rate
@@ -328,32 +330,41 @@ mingru_scan_kernel(const float *row, int splits, const void *bz, const void *bx,
     const int chunks = (n + MG_CT - 1) / MG_CT;
     const int fw = warp - 1;                           // which of the fill warps (the first warp walks)
     const float vbz = (live && bz) ? load_any(bz, b_dt, c) : 0.f, vbx = (live && bx) ? load_any(bx, b_dt, c) : 0.f;
-    float ra[MG_PER], rb[MG_PER], rg[MG_PER];          // a chunk's operands on their way: tokens fw, fw + MG_FILL, ...
+    // two chunks' operands on their way: tokens fw, fw + MG_FILL, ... of the chunk after next are requested before the
+    // next chunk's are used, so a read has a whole round (a walk and a fill) to arrive
+    float ra[2][MG_PER], rb[2][MG_PER], rg[2][MG_PER];
 
-    auto request = [&](int k) {
+    auto request = [&](int k, float *qa, float *qb, float *qg) {
+        // the first split's values are taken as they are: a register that is only loaded does not hold its thread up
+        // until it is used, so the reads of a product that is not split stay in flight behind this call
 #pragma unroll
-        for (int u = 0; u < MG_PER; u++) ra[u] = rb[u] = rg[u] = 0.f;
-        for (int s = 0; s < splits; s++) {
+        for (int u = 0; u < MG_PER; u++) {
+            const int i = k * MG_CT + fw + u * MG_FILL;
+            const bool ok = i < n && live;
+            const float *p = row + (size_t)(t0 + (ok ? i : 0)) * C3 + (live ? c : 0);
+            qa[u] = ok ? p[0] : 0.f; qb[u] = ok ? p[W] : 0.f; qg[u] = ok ? p[2 * (size_t)W] : 0.f;
+        }
+        for (int s = 1; s < splits; s++) {
 #pragma unroll
             for (int u = 0; u < MG_PER; u++) {
                 const int i = k * MG_CT + fw + u * MG_FILL;
                 if (i < n && live) {
                     const float *p = row + (size_t)s * plane + (size_t)(t0 + i) * C3 + c;
-                    ra[u] += p[0]; rb[u] += p[W]; rg[u] += p[2 * (size_t)W];
+                    qa[u] += p[0]; qb[u] += p[W]; qg[u] += p[2 * (size_t)W];
                 }
             }
         }
     };
-    auto finish = [&](int k) {
+    auto finish = [&](int k, const float *qa, const float *qb, const float *qg) {
         const int buf = k & 1;
 #pragma unroll
         for (int u = 0; u < MG_PER; u++) {
             const int j = fw + u * MG_FILL;
-            const float z = sigmoid_f(ra[u] + vbz), v = rb[u] + vbx, g = rg[u];
-            const float cand = v >= 0.f ? v + 0.5f : sigmoid_f(v);
+            const float z = sigmoid_fast(qa[u] + vbz), v = qb[u] + vbx, g = qg[u];
+            const float cand = v >= 0.f ? v + 0.5f : sigmoid_fast(v);
             s_a[buf][j][lane] = 1.0f - z;
             s_b[buf][j][lane] = z * cand;
-            s_g[buf][j][lane] = g * sigmoid_f(g);
+            s_g[buf][j][lane] = g * sigmoid_fast(g);
         }
     };
 
@@ -361,27 +372,36 @@ mingru_scan_kernel(const float *row, int splits, const void *bz, const void *bx,
     if (warp == 0) {
         if (live) S = state[(size_t)slot * slot_stride + c];
     } else {
-        request(0);
-        finish(0);
-        if (chunks > 1) request(1);
+        request(0, ra[0], rb[0], rg[0]);
+        if (chunks > 1) request(1, ra[1], rb[1], rg[1]);
+        finish(0, ra[0], rb[0], rg[0]);
+        if (chunks > 2) request(2, ra[0], rb[0], rg[0]);
     }
     __syncthreads();
-    for (int k = 0; k < chunks; k++) {
-        if (warp == 0) {
-            const int buf = k & 1, m = min(MG_CT, n - k * MG_CT);
-            if (live) {
-                TO *o = out + (size_t)(t0 + k * MG_CT) * W + c;
+    // (the loop is unrolled by two so that the register sets are named at compile time)
+    for (int k = 0; k < chunks; k += 2) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int kk = k + h;
+            if (kk < chunks) {
+                if (warp == 0) {
+                    const int buf = kk & 1, m = min(MG_CT, n - kk * MG_CT);
+                    if (live) {
+                        TO *o = out + (size_t)(t0 + kk * MG_CT) * W + c;
 #pragma unroll 4
-                for (int j = 0; j < m; j++) {
-                    S = fmaf(s_a[buf][j][lane], S, s_b[buf][j][lane]);
-                    o[(size_t)j * W] = from_f32<TO>(S * s_g[buf][j][lane]);
+                        for (int j = 0; j < m; j++) {
+                            S = fmaf(s_a[buf][j][lane], S, s_b[buf][j][lane]);
+                            o[(size_t)j * W] = from_f32<TO>(S * s_g[buf][j][lane]);
+                        }
+                    }
+                } else if (kk + 1 < chunks) {
+                    // chunk kk + 1 sits in set (kk + 1) & 1 = 1 - h; once used, that set takes chunk kk + 3
+                    finish(kk + 1, ra[1 - h], rb[1 - h], rg[1 - h]);
+                    if (kk + 3 < chunks) request(kk + 3, ra[1 - h], rb[1 - h], rg[1 - h]);
                 }
             }
-        } else if (k + 1 < chunks) {
-            finish(k + 1);
-            if (k + 2 < chunks) request(k + 2);
+            __syncthreads();
         }
-        __syncthreads();
     }
     if (warp == 0 && live) state[(size_t)slot * slot_stride + c] = S;
 }
