@@ -79,26 +79,32 @@ __device__ __forceinline__ void ln_block_sum2(float &a, float &b, float *red)
 // is made again here rather than passed between blocks), or, in the block of a request's first token of the step, the
 // request's last token's, which goes to the slot.  state [slots][slot_stride] float32.
 template <typename TO, int PER>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(PER <= 8 ? 512 : 1024)
 layernorm_shift_kernel(const float *x, const float *w, const float *mu, float eps, int center, float *state, size_t slot_stride,
                        const int32_t *token_seq, const int32_t *cu_tokens, const int32_t *seq_slots, int n_slots, TO *out, int T,
                        int E, int *err)
 {
     pdl_entry();
-    pdl_sync_small();
     __shared__ float red[64];
     const int t = blockIdx.x;
+    // the weights and the shift do not come from the kernel in front: fetch them while it finishes (rows of up to 4,096
+    // values; wider rows read them at the end, for want of registers)
+    constexpr bool EARLY = PER <= 8;
+    float wv[EARLY ? PER : 1], muv[EARLY ? PER : 1];
+    if (EARLY) {
+#pragma unroll
+        for (int j = 0; j < (EARLY ? PER : 1); j++) {
+            const int i = threadIdx.x + j * blockDim.x;
+            wv[j] = i < E ? w[i] : 0.f;
+            muv[j] = i < E ? mu[i] : 0.f;
+        }
+    }
+    pdl_sync_small();
     const int seq = token_seq[t];
     const int t0 = cu_tokens[seq], t_last = cu_tokens[seq + 1] - 1;
     const bool first = t == t0;
     const int t_other = first ? t_last : t - 1;
     const bool two = t_other != t;
-    float *st = nullptr;
-    if (first) {
-        const int slot = seq_slots[seq];
-        if (slot < 0 || slot >= n_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
-        st = state + (size_t)slot * slot_stride;
-    }
     const float *xa = x + (size_t)t * E, *xb = x + (size_t)t_other * E;
     float va[PER], vb[PER];
     float sa = 0.f, sb = 0.f;
@@ -107,6 +113,23 @@ layernorm_shift_kernel(const float *x, const float *w, const float *mu, float ep
         const int i = threadIdx.x + j * blockDim.x;
         va[j] = i < E ? xa[i] : 0.f;
         vb[j] = (two && i < E) ? xb[i] : 0.f;
+    }
+    float *st = nullptr;
+    float bef[EARLY ? PER : 1];
+    if (first) {
+        const int slot = seq_slots[seq];
+        if (slot < 0 || slot >= n_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
+        st = state + (size_t)slot * slot_stride;
+        if (EARLY) {
+#pragma unroll
+            for (int j = 0; j < (EARLY ? PER : 1); j++) {
+                const int i = threadIdx.x + j * blockDim.x;
+                bef[j] = i < E ? st[i] : 0.f;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
         sa += va[j];
         sb += vb[j];
     }
@@ -130,17 +153,17 @@ layernorm_shift_kernel(const float *x, const float *w, const float *mu, float ep
     for (int j = 0; j < PER; j++) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i >= E) continue;
-        const float wi = w[i];
+        const float wi = EARLY ? wv[EARLY ? j : 0] : w[i], mi = EARLY ? muv[EARLY ? j : 0] : mu[i];
         const float h = (va[j] - mean_a) * ra * wi;
         const float other = two ? (vb[j] - mean_b) * rb * wi : h;
         float before;
         if (first) {
-            before = st[i];
+            before = EARLY ? bef[EARLY ? j : 0] : st[i];
             st[i] = other;                           // the request's last row of the step (this one, if it is the only one)
         } else {
             before = other;
         }
-        out[(size_t)t * E + i] = from_f32<TO>(fmaf(before - h, mu[i], h));
+        out[(size_t)t * E + i] = from_f32<TO>(fmaf(before - h, mi, h));
     }
 }
 
@@ -394,12 +417,12 @@ extern "C" int hfb_layernorm_shift(const float *x, const float *w, const float *
     if (!x || !w || !mu || !state || !token_seq || !cu_tokens || !seq_slots || !out || !valid_dt(out_dt) || E <= 0 || slot_stride < E)
         return fail(HFB_EINVAL, "layernorm_shift: bad arguments (E=%d)", E);
     if (E > LNT_PER * 1024) return fail(HFB_ENOTSUP, "layernorm_shift: rows of %d values exceed %d", E, LNT_PER * 1024);
-    int threads = ((E + 7) / 8 + 31) / 32 * 32;           // eight values a thread where the row allows
-    if (threads > 1024) threads = 1024;
+    int threads = ((E + 7) / 8 + 31) / 32 * 32;           // eight values a thread for rows of up to 4,096, sixteen beyond
+    const bool few = threads <= 512;
+    if (!few) threads = ((E + 15) / 16 + 31) / 32 * 32;
 #define HFB_LNS(TY, PER) \
     g_launch_err = launch_pdl(layernorm_shift_kernel<TY, PER>, dim3(T), dim3(threads), 0, (cudaStream_t)s, x, w, mu, eps, center, state, \
                               (size_t)slot_stride, token_seq, cu_tokens, seq_slots, n_slots, (TY *)out, T, E, error_word())
-    const bool few = E <= 8 * threads;
     if (out_dt == HFB_F32) { if (few) HFB_LNS(float, 8); else HFB_LNS(float, LNT_PER); }
     else { if (few) HFB_LNS(__nv_bfloat16, 8); else HFB_LNS(__nv_bfloat16, LNT_PER); }
 #undef HFB_LNS
