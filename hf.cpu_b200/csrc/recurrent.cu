@@ -406,6 +406,34 @@ mingru_scan_kernel(const float *row, int splits, const void *bz, const void *bx,
     if (warp == 0 && live) state[(size_t)slot * slot_stride + c] = S;
 }
 
+
+// The same for a step in which every request brings one token (row s is request s): one thread per (request, channel),
+// nothing to walk along.  The operations on S are those of the kernel above, in the same order.
+template <typename TO>
+__global__ void mingru_step_kernel(const float *row, int splits, const void *bz, const void *bx, int b_dt, float *state,
+                                   size_t slot_stride, const int32_t *seq_slots, int n_slots, TO *out, int T, int W, int *err)
+{
+    pdl_entry();
+    pdl_sync_small();
+    const size_t C3 = 3 * (size_t)W, plane = (size_t)T * C3;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)T * W; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / W), c = (int)(i % W);
+        const int slot = seq_slots[t];
+        if (slot < 0 || slot >= n_slots) { atomicOr(err, HFB_ERR_SLOT); continue; }
+        const float *p = row + (size_t)t * C3 + c;
+        float a = p[0], b = p[W], g = p[2 * (size_t)W];
+        for (int s = 1; s < splits; s++) {
+            a += p[(size_t)s * plane]; b += p[(size_t)s * plane + W]; g += p[(size_t)s * plane + 2 * (size_t)W];
+        }
+        float *st = state + (size_t)slot * slot_stride + c;
+        const float z = sigmoid_fast(a + (bz ? load_any(bz, b_dt, c) : 0.f)), v = b + (bx ? load_any(bx, b_dt, c) : 0.f);
+        const float cand = v >= 0.f ? v + 0.5f : sigmoid_fast(v);
+        const float S = fmaf(1.0f - z, *st, z * cand);
+        *st = S;
+        out[i] = from_f32<TO>(S * (g * sigmoid_fast(g)));
+    }
+}
+
 }  // namespace hfb
 
 using namespace hfb;
@@ -500,6 +528,17 @@ extern "C" int hfb_mingru_scan(const float *row, int splits, const void *bz, con
         ((bz || bx) && !valid_dt(b_dt)))
         return fail(HFB_EINVAL, "mingru_scan: bad arguments (W=%d)", W);
     if (S > 65535) return fail(HFB_ENOTSUP, "mingru_scan: %d requests exceed the grid limit", S);
+    if (T == S) {
+        // every request brings one token
+        const int blocks = rec_blocks((size_t)T * W);
+        if (out_dt == HFB_F32)
+            g_launch_err = launch_pdl(mingru_step_kernel<float>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, row, splits, bz, bx, b_dt, state,
+                                      (size_t)slot_stride, seq_slots, n_slots, (float *)out, T, W, error_word());
+        else
+            g_launch_err = launch_pdl(mingru_step_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, row, splits, bz, bx, b_dt,
+                                      state, (size_t)slot_stride, seq_slots, n_slots, (__nv_bfloat16 *)out, T, W, error_word());
+        return check_pdl_launch(g_launch_err, "mingru_step");
+    }
     const dim3 grid((W + MG_CH - 1) / MG_CH, S);
     const dim3 block((MG_FILL + 1) * 32);
     if (out_dt == HFB_F32)
