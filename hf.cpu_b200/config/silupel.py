@@ -119,7 +119,7 @@ class SilupelConfig(ModelConfig):
         loop = _obj(d, "loop", "", required=False)
         lp: Dict[str, int] = {}
         if loop is not None:
-            lp = {"start": take_int(loop, "start", lo=0), "stop": take_int(loop, "stop", lo=0), "times": take_int(loop, "times", lo=1)}
+            lp = {"start": take_int(loop, "start", lo=0), "stop": take_int(loop, "stop", lo=0), "times": take_int(loop, "times", lo=0)}
             if not lp["start"] <= lp["stop"] <= len(out):
                 raise ConfigError(f"config.json: loop: layers {lp['start']} .. {lp['stop']} are not a stretch of the {len(out)} layers")
         eos = d.get("eos_token_id", [])
